@@ -1,0 +1,112 @@
+"""Declarative description of a decoder: what each part is and how layers are arranged.
+
+An architecture turns its typed configuration into one ``ModelSpec``. Every size
+and constant a part needs is a field of its spec, so no part knows which model it
+is in; ``kind`` selects the implementation from the part registries, layer by
+layer, so one model may mix different mixers and feed-forwards. The order in
+which layers run is data as well (``run_order``): an entry may name a layer twice
+or let a layer read another layer's cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    """One checkpoint tensor a part wants.
+
+    role: 'matrix' and 'table' are kept in the engine dtype (bfloat16 or float32),
+    'vector' is always float32 (biases, norm parameters), 'int' is int32.
+    ``stored_in_out``: the checkpoint holds the matrix as [in, out] (GPT-2 Conv1D);
+    the device copy is always [out, in], K-contiguous.
+    """
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    stored_in_out: bool = False
+
+
+@dataclass(frozen=True)
+class NormSpec:
+    kind: str            # 'layernorm'
+    width: int
+    eps: float
+    weight: str          # checkpoint names
+    bias: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class PositionSpec:
+    kind: str            # 'learned'
+    n_positions: int
+    width: int
+    table: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    kind: str            # 'attention'
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    scale: float         # multiplies q.k (already includes any per-layer factor)
+    window: Optional[int]  # None = all earlier keys; n = the query and the n-1 keys before it
+    qkv_weight: str
+    qkv_bias: Optional[str]
+    out_weight: str
+    out_bias: Optional[str]
+    stored_in_out: bool = False
+
+
+@dataclass(frozen=True)
+class DenseFeedForwardSpec:
+    kind: str            # 'dense'
+    width: int
+    inner: int
+    activation: str      # 'gelu_new' | 'gelu'
+    up_weight: str
+    up_bias: Optional[str]
+    down_weight: str
+    down_bias: Optional[str]
+    stored_in_out: bool = False
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    arrangement: str     # 'pre_norm'
+    mixer: object
+    feed_forward: object
+    norm1: object
+    norm2: object
+
+
+@dataclass(frozen=True)
+class RunEntry:
+    """One stop in the forward pass: run ``layer`` with the cache of ``cache_of``."""
+    layer: int
+    cache_of: Optional[int] = None
+
+    @property
+    def cache_layer(self) -> int:
+        return self.layer if self.cache_of is None else self.cache_of
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    vocab_size: int
+    width: int
+    max_positions: int
+    token_table: str                  # checkpoint name of the token embedding
+    position: object                  # a position-encoding spec
+    layers: Tuple[LayerSpec, ...]
+    run_order: Tuple[RunEntry, ...]
+    final_norm: object
+    head_weight: Optional[str] = None  # None: the LM head is the token table (tied)
+    eos_token_ids: Tuple[int, ...] = ()
+    ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)   # regexes of tensors to drop
+    tied_duplicates: Tuple[Tuple[str, str], ...] = field(default_factory=tuple)  # (name, must equal)
+    optional_prefix: str = ""          # e.g. 'transformer.': stripped from every name when present

@@ -1,0 +1,34 @@
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+if str(ROOT / "tests") not in sys.path:
+    sys.path.insert(0, str(ROOT / "tests"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+# the two tiny configurations differ in every size and option
+TINY_A = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 64, "n_head": 4, "n_inner": None, "vocab_size": 512, "n_positions": 128,
+    "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_by_inverse_layer_idx": False,
+}
+TINY_B = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 3, "n_embd": 96, "n_head": 2, "n_inner": 320, "vocab_size": 1000, "n_positions": 256,
+    "layer_norm_epsilon": 1e-6, "activation_function": "gelu",
+    "scale_attn_by_inverse_layer_idx": True,
+}
+
+
+@pytest.fixture(scope="session")
+def tiny_configs():
+    return {"A": dict(TINY_A), "B": dict(TINY_B)}

@@ -1,0 +1,158 @@
+"""A plain, slow GPT-2: whole sequences, no cache, one function per part.
+
+It shares no code with the product path: it reads config.json and model.safetensors
+itself and computes with ordinary tensor arithmetic on the CPU (float64 by default,
+so that it is the more exact side of every comparison). Each function cites the
+reference lines its formula comes from. The reference's own model code was run once
+on the CPU against this file (tests/golden/make_golden.py); the two options the
+reference rejects (exact-erf gelu and scaling by inverse layer index,
+damendaemon/config.py:301-303) rest on their formulas alone.
+"""
+from __future__ import annotations
+
+import json
+import math
+import struct
+from pathlib import Path
+
+import numpy as np
+import torch
+
+_NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64}
+
+
+def read_folder(folder, dtype=torch.float64):
+    """(config dict, {name without 'transformer.': tensor of dtype})."""
+    folder = Path(folder)
+    config = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n])
+    tensors = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        b, e = meta["data_offsets"]
+        chunk = raw[8 + n + b:8 + n + e]
+        if meta["dtype"] == "BF16":
+            # bfloat16 is the upper half of a float32
+            u16 = np.frombuffer(chunk, dtype=np.uint16).astype(np.uint32) << 16
+            arr = u16.view(np.float32)
+        else:
+            arr = np.frombuffer(chunk, dtype=_NP[meta["dtype"]])
+        t = torch.from_numpy(arr.copy()).reshape(meta["shape"])
+        tensors[name.removeprefix("transformer.")] = t.to(dtype) if t.is_floating_point() else t
+    return config, tensors
+
+
+def embed(ids, wte, wpe):
+    """x[t] = wte[ids[t]] + wpe[t]  (damendaemon/gpt2.py:46; positions are arange, damendaemon/qwen2.py:866)."""
+    return wte[ids] + wpe[torch.arange(len(ids))]
+
+
+def layer_norm(x, gamma, beta, eps):
+    """(x - mean) / sqrt(biased var + eps) * gamma + beta  (damendaemon/starcoder.py:53-55)."""
+    mean = x.mean(-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(-1, keepdim=True)
+    return (x - mean) / torch.sqrt(var + eps) * gamma + beta
+
+
+def conv1d(x, weight_in_out, bias):
+    """y = x @ W + b with W stored [in, out]  (damendaemon/gpt2.py:32-37,48)."""
+    return x @ weight_in_out + bias
+
+
+def causal_attention(q, k, v, scale, window=None):
+    """softmax(q k^T * scale, keys j <= i [and j > i - window]) v, per head.
+
+    q, k, v: [T, H, d]. Scale d^-0.5 and the causal rule are damendaemon/kernels.py:147,263
+    and damendaemon/qwen2.py:769-770; softmax with the maximum subtracted,
+    damendaemon/kernels.py:168-178.
+    """
+    T = q.shape[0]
+    scores = torch.einsum("ihd,jhd->hij", q, k) * scale
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    visible = j <= i
+    if window is not None:
+        visible = visible & (j > i - window)
+    scores = scores.masked_fill(~visible, float("-inf"))
+    scores = scores - scores.max(-1, keepdim=True).values
+    p = torch.exp(scores)
+    p = p / p.sum(-1, keepdim=True)
+    return torch.einsum("hij,jhd->ihd", p, v)
+
+
+def gelu_new(u):
+    """0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)))  (damendaemon/gpt2.py:63, approximate='tanh')."""
+    return 0.5 * u * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (u + 0.044715 * u ** 3)))
+
+
+def gelu_erf(u):
+    """0.5 u (1 + erf(u / sqrt 2)): the exact form, which the reference rejects (damendaemon/config.py:301)."""
+    return 0.5 * u * (1.0 + torch.erf(u / math.sqrt(2.0)))
+
+
+def attention_block(x, w, prefix, n_head, scale):
+    """c_attn, split in thirds, heads, attention, c_proj  (damendaemon/gpt2.py:48-61)."""
+    T, h = x.shape
+    qkv = conv1d(x, w[prefix + "attn.c_attn.weight"], w[prefix + "attn.c_attn.bias"])
+    q, k, v = (part.reshape(T, n_head, h // n_head) for part in qkv.split(h, dim=-1))
+    o = causal_attention(q, k, v, scale).reshape(T, h)
+    return conv1d(o, w[prefix + "attn.c_proj.weight"], w[prefix + "attn.c_proj.bias"])
+
+
+def mlp_block(x, w, prefix, activation):
+    """c_fc, activation, c_proj  (damendaemon/gpt2.py:62-64)."""
+    u = conv1d(x, w[prefix + "mlp.c_fc.weight"], w[prefix + "mlp.c_fc.bias"])
+    g = gelu_new(u) if activation == "gelu_new" else gelu_erf(u)
+    return conv1d(g, w[prefix + "mlp.c_proj.weight"], w[prefix + "mlp.c_proj.bias"])
+
+
+def logits_of(config, w, ids):
+    """Logits at every position of one whole sequence, [T, vocab]  (damendaemon/gpt2.py:42-66)."""
+    ids = torch.as_tensor(ids, dtype=torch.long)
+    h, H = config["n_embd"], config["n_head"]
+    eps = config.get("layer_norm_epsilon", 1e-5)
+    activation = config.get("activation_function", "gelu_new")
+    x = embed(ids, w["wte.weight"], w["wpe.weight"])
+    for i in range(config["n_layer"]):
+        p = f"h.{i}."
+        scale = (h // H) ** -0.5
+        if config.get("scale_attn_by_inverse_layer_idx", False):
+            scale = scale / (i + 1)
+        x = x + attention_block(layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps), w, p, H, scale)
+        x = x + mlp_block(layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps), w, p, activation)
+    x = layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps)
+    return x @ w["wte.weight"].t()          # tied head, no bias (damendaemon/gpt2.py:18,66)
+
+
+class PlainGpt2:
+    def __init__(self, folder, dtype=torch.float64):
+        self.config, self.w = read_folder(folder, dtype)
+
+    def logits(self, ids):
+        return logits_of(self.config, self.w, ids)
+
+    def greedy(self, prompt, n_new):
+        ids = list(prompt)
+        for _ in range(n_new):
+            if len(ids) >= self.config["n_positions"]:
+                break
+            ids.append(int(self.logits(ids)[-1].argmax()))
+        return ids[len(prompt):]
+
+
+def sample_token(logits_row, temperature, u):
+    """The engine's sampling rule, restated: greedy = first maximum; else inverse CDF.
+
+    p = softmax(logits / T) in token-id order, c = cumulative sum, the token is the first
+    index whose c exceeds u * c[-1] (the reference draws u from a per-request
+    random.Random and searches the normalised CDF, damendaemon/sampling.py:131-177).
+    """
+    row = torch.as_tensor(logits_row, dtype=torch.float64)
+    if not temperature:
+        return int(row.argmax())
+    z = (row - row.max()) / temperature
+    c = torch.exp(z).cumsum(0)
+    return int(min(torch.searchsorted(c, torch.tensor(u * float(c[-1]), dtype=torch.float64), right=True), len(row) - 1))
