@@ -1,0 +1,31 @@
+// Error reporting of the C ABI: every launcher returns 0 or records one message.
+#include "common.cuh"
+#include <stdarg.h>
+#include <stdio.h>
+
+static thread_local char g_message[512] = "";
+
+int dd_fail(const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_message, sizeof(g_message), fmt, args);
+    va_end(args);
+    return 1;
+}
+
+int dd_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return dd_fail("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+DD_API const char* dd_last_error() { return g_message; }
+
+// Compute capability of the current device as major*10+minor, or a negative CUDA error.
+DD_API int dd_device_arch() {
+    int dev = 0, major = 0, minor = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    return major * 10 + minor;
+}

@@ -1,0 +1,43 @@
+"""The description of one step as the kernels see it: flattened tokens with per-token
+position and entry, per-entry bookkeeping, the rows whose logits are wanted, and the
+block tables of the entries, all int32 on the device (one host-to-device copy a step)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from .. import kernels
+
+
+@dataclass
+class StepContext:
+    n_tokens: int
+    n_entries: int
+    n_wanted: int
+    token_ids: object          # int32 [N]
+    positions: object          # int32 [N]   absolute position of each token in its request
+    token_entry: object        # int32 [N]   which entry (row of the block tables) a token belongs to
+    want_rows: object          # int32 [M]   flattened token indices whose logits are wanted
+    entry_slot: object         # int32 [E]   the request's state slot
+    entry_start: object        # int32 [E+1] first flattened token of each entry
+    entry_pos0: object         # int32 [E]   tokens the request held before this step
+    block_tables: dict         # cache group name -> int32 [E, max_blocks]
+    host: dict = field(default_factory=dict)   # the same lists on the host, for parts that plan there
+    decode_only: bool = False
+    split_context: int = 0     # context length the key splits are planned for
+    runtime: object = None
+    sm_count: int = 148
+
+    def block_table(self, group):
+        return self.block_tables[group.name]
+
+    def key_splits(self, n_heads):
+        """How many pieces each row's keys are cut into so that a decode-only step fills the GPU."""
+        if not self.decode_only:
+            return 1
+        want = (self.sm_count * 16) // max(1, self.n_tokens * n_heads)
+        return max(1, min(want, (self.split_context + 63) // 64, 32))
+
+    def attention(self, q, kv, table, n_heads, scale, window=None):
+        """Paged causal attention of this step's tokens over the cache."""
+        return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
+                                      n_splits=self.key_splits(n_heads))

@@ -1,0 +1,215 @@
+"""Python face of the hand-written CUDA kernels (ctypes over the extern "C" launchers).
+
+Every function takes CUDA tensors and launches on the current stream. There is no CPU
+path and no library stand-in: a tensor that is not on a CUDA device, or a library that
+cannot be built or loaded, raises ``KernelError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2}
+
+_c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "core": {
+        "dd_device_arch": [],
+        "dd_embed": [_c_void] * 5 + [_c_int] * 5 + [_c_void, _c_void],
+        "dd_layernorm": [_c_void] * 5 + [_c_int, _c_int, _c_float, _c_int, _c_void],
+        "dd_gemm_simt": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
+        "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 6 + [_c_void, _c_void],
+        "dd_attention_rows": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
+                             + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void],
+        "dd_sample": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
+    },
+    "tensor": {},
+}
+
+_libs, _lock = {}, threading.Lock()
+
+
+def library(name):
+    """Load (building first if needed) one of the kernel libraries."""
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    with _lock:
+        if name in _libs:
+            return _libs[name]
+        try:
+            path = build.build_library(name)
+            lib = ctypes.CDLL(str(path))
+        except (build.BuildError, OSError) as error:
+            raise KernelError(f"the '{name}' CUDA kernels are not available ({error}); "
+                              "this engine has no CPU or library fallback") from error
+        lib.dd_last_error.restype = ctypes.c_char_p
+        for fn, args in _SIGNATURES[name].items():
+            f = getattr(lib, fn)
+            f.argtypes, f.restype = args, _c_int
+        _libs[name] = lib
+        return lib
+
+
+def _call(lib, fn, *args):
+    code = getattr(lib, fn)(*args)
+    if code:
+        raise KernelError(lib.dd_last_error().decode())
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t):
+    if t is torch.float32 or t == torch.float32:
+        return F32
+    if t == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {t}")
+
+
+def _ptr(t, name="tensor", dtype=None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on CUDA only (no CPU fallback)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    return t.data_ptr()
+
+
+def _rows(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-D with contiguous rows, has shape {tuple(t.shape)} strides {t.stride()}")
+    return t
+
+
+_error_flags = {}
+
+
+def error_flag(device):
+    """One int32 per device that kernels OR error bits into (1 bad token/position, 2 bad page
+    on store, 4 bad page on read, 8 a bounded wait ran out)."""
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def read_error_flag(device):
+    flag = error_flag(device)
+    value = int(flag.item())
+    if value:
+        flag.zero_()
+    return value
+
+
+# ---------------------------------------------------------------- kernels
+
+def embed(ids, positions, token_table, position_table=None, out=None):
+    n, width = ids.numel(), token_table.shape[1]
+    if out is None:
+        out = torch.empty((n, width), dtype=torch.float32, device=ids.device)
+    if position_table is not None and position_table.dtype != token_table.dtype:
+        raise KernelError("token and position tables must have one dtype")
+    _call(library("core"), "dd_embed", _ptr(ids, "ids", torch.int32), _ptr(positions, "positions", torch.int32),
+          _ptr(token_table, "token table"), _ptr(position_table, "position table"), _ptr(out, "out", torch.float32),
+          n, width, token_table.shape[0], 0 if position_table is None else position_table.shape[0],
+          _dt(token_table.dtype), _ptr(error_flag(ids.device)), _stream())
+    return out
+
+
+def layernorm(x, gamma, beta, eps, out_dtype, row_index=None, out=None):
+    _rows(x, "x")
+    rows = x.shape[0] if row_index is None else row_index.numel()
+    width = x.shape[1]
+    if not x.is_contiguous():
+        raise KernelError("layernorm input must be contiguous")
+    if out is None:
+        out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    _call(library("core"), "dd_layernorm", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32),
+          _ptr(gamma, "gamma", torch.float32), _ptr(beta, "beta", torch.float32), _ptr(out, "out", out_dtype),
+          rows, width, float(eps), _dt(out_dtype), _stream())
+    return out
+
+
+def gemm_simt(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None):
+    """act(a @ w.T + bias) (+ residual) with CUDA-core float32 multiply-add. a [M,K], w [N,K]."""
+    _rows(a, "a"), _rows(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or a.dtype != w.dtype:
+        raise KernelError(f"gemm: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _rows(out, "out")
+    if residual is not None:
+        _rows(residual, "residual")
+    _call(library("core"), "dd_gemm_simt", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(0),
+          _ptr(bias, "bias", torch.float32), _ptr(residual, "residual", torch.float32),
+          0 if residual is None else residual.stride(0), _ptr(out, "out", out_dtype), out.stride(0),
+          M, N, K, ACTIVATIONS[activation], _dt(a.dtype), _dt(out_dtype), _stream())
+    return out
+
+
+def kv_store(k, v, token_entry, positions, block_table, cache, n_tokens=None):
+    """k, v: [N, kv_heads*head_dim] views (row stride free); cache [pages, 2, kv_heads, page, head_dim]."""
+    n_pages, _, kv_heads, page_size, head_dim = cache.shape
+    if k.stride(0) != v.stride(0) or k.stride(1) != 1 or v.stride(1) != 1 or k.dtype != cache.dtype:
+        raise KernelError("kv_store: k and v must be row views of one buffer in the cache dtype")
+    if k.shape[1] != kv_heads * head_dim or not cache.is_contiguous():
+        raise KernelError("kv_store: shapes do not fit the cache")
+    _call(library("core"), "dd_kv_store", _ptr(k, "k"), _ptr(v, "v"), k.stride(0),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
+          _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(cache, "cache"),
+          n_pages, kv_heads, page_size, head_dim, k.shape[0] if n_tokens is None else n_tokens, _dt(cache.dtype),
+          _ptr(error_flag(k.device)), _stream())
+
+
+def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None):
+    """General paged causal attention. q: [N, n_heads*head_dim] view; returns [N, n_heads*head_dim]."""
+    n_pages, _, kv_heads, page_size, head_dim = cache.shape
+    n = q.shape[0]
+    if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != cache.dtype or not cache.is_contiguous():
+        raise KernelError("attention: q does not fit the cache")
+    if out is None:
+        out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    _call(library("core"), "dd_attention_rows", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
+          _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
+          _ptr(part_o), _ptr(part_ml), n, n_heads, kv_heads, head_dim, page_size, n_pages,
+          0 if window is None else int(window), float(scale), int(n_splits), _dt(q.dtype),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
+def sample(logits, temperature=None, uniform=None, out=None):
+    """Row-wise token choice: argmax where temperature is 0 (or None), else an inverse-CDF draw
+    with the given uniform numbers. Returns int32 ids, -1 for rows without a finite maximum."""
+    _rows(logits, "logits")
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if temperature is not None and uniform is None:
+        raise KernelError("sampling with a temperature needs uniform draws")
+    _call(library("core"), "dd_sample", _ptr(logits, "logits", torch.float32), logits.stride(0), rows, vocab,
+          _ptr(temperature, "temperature", torch.float32), _ptr(uniform, "uniform", torch.float64),
+          _ptr(out, "out", torch.int32), _stream())
+    return out

@@ -1,0 +1,74 @@
+"""What a part must look like. Parts are chosen by the spec's ``kind`` and built as
+``cls(spec, weights, runtime)``; none of them knows which model it is in.
+
+``weights``  {checkpoint name: device tensor}, already checked and placed.
+``runtime``  a ``Runtime`` (below): engine dtype, device and kernel choices.
+``ctx``      the step's ``StepContext`` (engine/context.py): flattened token metadata
+             on the device, block tables per cache group, scratch.
+``cache``    a ``LayerCache`` (cache/manager.py): ``kv`` pages of this layer
+             [pages, 2, kv_heads, page_size, head_dim], ``group`` (its block table is
+             ``ctx.block_table(cache.group)``), ``state`` rows [max_requests, ...].
+
+Norm              tensor_decls(spec); forward(x_f32 [N,width], row_index=None) -> [N,width] engine dtype
+PositionEncoding  tensor_decls(spec); embedding_table() -> table or None (added to the token
+                  embedding by the fused embedding kernel); on_embedding(x, ctx) -> x for
+                  encodings that act there without a table; on_query_key(q, k, ctx) -> (q, k)
+                  for encodings that rotate or bias inside the mixer
+Mixer             tensor_decls(spec); cache_needs(spec) -> [PagedKeyValues | RequestState];
+                  forward(y, residual, ctx, cache, position) -> residual + mix(y)   (float32 [N,width])
+FeedForward       tensor_decls(spec); forward(y, residual, ctx) -> residual + ff(y)
+Arrangement       cls(layer_spec, norm1, mixer, norm2, feed_forward);
+                  forward(x, ctx, cache, position) -> x
+
+``residual`` is the float32 residual stream; a part returns the updated stream and may
+write it in place (the GEMM epilogues add into it).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class Runtime:
+    dtype: torch.dtype            # engine dtype: torch.bfloat16 or torch.float32
+    device: torch.device
+    gemm: str = "auto"            # 'auto' | 'simt' | 'tcgen05'
+    attention: str = "auto"       # 'auto' | 'rows'
+
+
+class Part:
+    @staticmethod
+    def tensor_decls(spec):
+        return []
+
+
+class Mixer(Part):
+    @staticmethod
+    def cache_needs(spec):
+        return []
+
+    def forward(self, y, residual, ctx, cache, position):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, y, residual, ctx):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x, row_index=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def embedding_table(self):
+        return None
+
+    def on_embedding(self, x, ctx):
+        return x
+
+    def on_query_key(self, q, k, ctx):
+        return q, k
