@@ -1,0 +1,148 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way of
+cutting the work: whole, last 32 tokens one by one, portions of changing size, and mixed with
+so few pages that they are used again."""
+import pytest
+import torch
+
+from conftest import TINY_A, TINY_B
+from model_tools import make_model, random_requests
+from plain_gpt2 import PlainGpt2
+from trace_tools import mixed_steps, portion_steps, run_trace, tail_steps, whole_steps
+
+pytestmark = pytest.mark.gpu
+
+CASES = {"A": (TINY_A, 0, [5, 17, 33, 100, 128, 64]), "B": (TINY_B, 1, [1, 9, 64, 200, 256, 77])}
+# float32: the engine's contract (1e-4). bfloat16: activations are rounded to 8 bits of mantissa
+# (relative 2^-9) a dozen times per layer on logits of size ~1.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, (config, seed, lengths) in CASES.items():
+        for dtype in ("float32", "bfloat16"):
+            folder = make_model(root / f"{name}-{dtype}", config, seed, dtype)
+            requests = random_requests(config, lengths, 100 + seed)
+            plain = PlainGpt2(folder)
+            want = {r: plain.logits(t).float() for r, t in requests.items()}
+            out[name, dtype] = (folder, config, requests, want)
+    return out
+
+
+def engine_for(folder, dtype, kv_tokens, page_size, poison=True):
+    from damendaemon_b200.engine import Engine
+    engine = Engine(folder, dtype=dtype, kv_tokens=kv_tokens, page_size=page_size, max_requests=8)
+    if poison:
+        for g in engine.cache.groups:
+            g.arena.fill_(float("nan"))      # whatever was never written must never be read
+    return engine
+
+
+def replay(engine, builder):
+    from damendaemon_b200.engine import StepEntry
+    got = {}
+    for s in builder.steps:
+        entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]
+        if entries:
+            logits = engine.step(entries).cpu()
+            for (request, position), row in zip(builder.where[s["step"]], logits):
+                got.setdefault(request, {})[position] = row
+        for r in s["end"]:
+            engine.finish(r)
+        engine.cache.check()
+    return got
+
+
+def compare(got, want, tol, what):
+    worst = 0.0
+    for r, rows in got.items():
+        for p, row in rows.items():
+            assert torch.isfinite(row).all(), f"{what}: non-finite logits at request {r} position {p}"
+            err = (row - want[r][p]).abs().max().item()
+            worst = max(worst, err)
+            assert err < tol, f"{what}: request {r} position {p} differs by {err:.3e} (first wrong place)"
+    for r in want:
+        assert set(got[r]) == set(range(len(want[r]))), f"{what}: request {r} misses positions"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cuttings(models, name, dtype, mode):
+    folder, config, requests, want = models[name, dtype]
+    page = 16 if name == "A" else 8
+    if mode == "mixed":
+        builder, peak = mixed_steps(requests, seed=3)
+        kv = peak
+    else:
+        builder = {"whole": whole_steps, "tail": tail_steps, "portions": portion_steps}[mode](requests)
+        kv = 64 * ((config["n_positions"] + 63) // 64)
+    engine = engine_for(folder, dtype, kv, page)
+    got = replay(engine, builder)
+    compare(got, want, TOL[dtype], f"{name} {dtype} {mode}")
+    assert engine.cache.used_tokens == 0 and not engine.live_requests()
+    if mode == "mixed":
+        total = sum(len(t) for t in requests.values())
+        assert engine.cache.groups[0].pool.n_pages * page < total, "the pool is too large for pages to be used again"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_float32_cuttings_agree_to_rounding(models, dtype):
+    """The same position under different cuttings: equal beyond rounding, far inside the tolerance to plain."""
+    folder, config, requests, want = models["A", dtype]
+    a = replay(engine_for(folder, dtype, 512, 16), whole_steps(requests))
+    b = replay(engine_for(folder, dtype, 512, 16), portion_steps(requests))
+    worst = max((a[r][p] - b[r][p]).abs().max().item() for r in a for p in a[r])
+    assert worst < (2e-6 if dtype == "float32" else 3e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(models, dtype):
+    """One token at a time from the very first token up to the model's last position."""
+    from damendaemon_b200.engine import StepEntry, StepError
+    folder, config, requests, want = models["B", dtype]
+    tokens = requests["r4"]                 # 256 tokens = n_positions
+    engine = engine_for(folder, dtype, 256, 8)
+    for p, t in enumerate(tokens):
+        row = engine.step([StepEntry("x", [t], [0])]).cpu()[0]
+        err = (row - want["r4"][p]).abs().max().item()
+        assert err < TOL[dtype], f"position {p}: {err:.3e}"
+    # the learned positions end here: one more token must be refused and change nothing
+    before = engine.length("x")
+    with pytest.raises(StepError, match="positions"):
+        engine.step([StepEntry("x", [1], [0])])
+    assert engine.length("x") == before == 256
+    engine.finish("x")
+    engine.cache.check()
+
+
+def test_step_validation_changes_nothing(models):
+    from damendaemon_b200.cache import PageCapacityError
+    from damendaemon_b200.engine import StepEntry, StepError
+    folder, config, requests, want = models["A", "float32"]
+    engine = engine_for(folder, "float32", 64, 16)
+    engine.step([StepEntry("a", [1, 2, 3])])
+    for bad in ([StepEntry("a", [1]), StepEntry("a", [2])], [StepEntry("b", [])], [StepEntry("b", [512])],
+                [StepEntry("b", [-1])], [StepEntry("b", [1, 2], [2])], [StepEntry("b", [1] * 129)], []):
+        with pytest.raises(StepError):
+            engine.step(bad)
+        assert engine.live_requests() == ["a"] and engine.length("a") == 3
+    with pytest.raises(PageCapacityError):
+        engine.step([StepEntry("a", [1]), StepEntry("b", [1] * 60)])     # 64 tokens of pages in all
+    assert engine.live_requests() == ["a"] and engine.length("a") == 3
+    engine.cache.check()
+    none = engine.step([StepEntry("a", [4, 5])])
+    assert tuple(none.shape) == (0, 512)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype, tmp_path):
+    """The replay program itself, as a user runs it: mixed trace, few pages."""
+    folder, config, requests, want = models["A", dtype]
+    builder, peak = mixed_steps(requests, seed=11)
+    outputs = run_trace(folder, dtype, builder.steps, tmp_path / "out", max_tokens=peak, page_size=16)
+    got = {r: {p: torch.from_numpy(row.copy()) for p, row in rows.items()} for r, rows in builder.collect(outputs).items()}
+    compare(got, want, TOL[dtype], f"trace_run {dtype}")

@@ -1,0 +1,205 @@
+"""Each CUDA-core kernel alone against a plain float64 reference, at sizes the engine's tiny
+models do not use (widths and vocabularies that are no power of two, grouped heads, windows)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from damendaemon_b200 import kernels
+    kernels.library("core")
+    return kernels
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(K, dtype):
+    g = torch.Generator().manual_seed(0)
+    wte = torch.randn(301, 80, generator=g).to(dtype).to(DEV)
+    wpe = torch.randn(77, 80, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, 301, (50,), generator=g, dtype=torch.int32).to(DEV)
+    pos = torch.randint(0, 77, (50,), generator=g, dtype=torch.int32).to(DEV)
+    out = K.embed(ids, pos, wte, wpe)
+    ref = wte[ids.long()].float() + wpe[pos.long()].float()
+    assert out.dtype == torch.float32 and torch.equal(out, ref)
+    assert torch.equal(K.embed(ids, pos, wte, None), wte[ids.long()].float())
+    assert K.read_error_flag(DEV) == 0
+    bad = ids.clone(); bad[3] = 301
+    K.embed(bad, pos, wte, wpe)
+    assert K.read_error_flag(DEV) == 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [100, 1600])
+def test_layernorm(K, dtype, width):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(9, width, generator=g) * 3 + 5).to(DEV)       # a large mean shows a one-pass variance
+    gamma, beta = torch.randn(width, generator=g).to(DEV), torch.randn(width, generator=g).to(DEV)
+    eps = 1e-6
+    x64 = x.double()
+    ref = (x64 - x64.mean(-1, keepdim=True)) / torch.sqrt(x64.var(-1, unbiased=False, keepdim=True) + eps) * gamma.double() + beta.double()
+    out = K.layernorm(x, gamma, beta, eps, dtype)
+    assert out.dtype == dtype
+    assert (out.double() - ref).abs().max() < (1e-5 if dtype == torch.float32 else 4e-2)
+    rows = torch.tensor([7, 2, 2], dtype=torch.int32, device=DEV)
+    picked = K.layernorm(x, gamma, beta, eps, dtype, row_index=rows)
+    assert torch.equal(picked, out[rows.long()])
+    nobeta = K.layernorm(x, gamma, None, eps, torch.float32)
+    assert (nobeta.double() - (ref - beta.double())).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(37, 53, 45), (1, 130, 96), (70, 64, 320)])
+def test_gemm_simt(K, dtype, shape):
+    M, N, Kd = shape
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(M, Kd, generator=g).to(dtype).to(DEV)
+    w = torch.randn(N, Kd, generator=g).to(dtype).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    res = torch.randn(M, N, generator=g).to(DEV)
+    base = a.double() @ w.double().t()
+    t = 1e-4 if dtype == torch.float32 else 1e-1
+    out = K.gemm_simt(a, w)
+    assert out.dtype == dtype and (out.double() - base).abs().max() < t
+    u = base + bias.double()
+    gelu_new = 0.5 * u * (1 + torch.tanh(math.sqrt(2 / math.pi) * (u + 0.044715 * u ** 3)))
+    gelu_erf = 0.5 * u * (1 + torch.erf(u / math.sqrt(2)))
+    assert (K.gemm_simt(a, w, bias, activation="gelu_new").double() - gelu_new).abs().max() < t
+    assert (K.gemm_simt(a, w, bias, activation="gelu").double() - gelu_erf).abs().max() < t
+    stream = res.clone()
+    got = K.gemm_simt(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream)
+    assert got.data_ptr() == stream.data_ptr()
+    assert (stream.double() - (u + res.double())).abs().max() < (1e-4 if dtype == torch.float32 else 1e-4 + 0)
+    # a row's result does not depend on the other rows of the batch
+    alone = K.gemm_simt(a[3:4].contiguous() if M > 3 else a, w, bias)
+    assert torch.equal(alone[0], K.gemm_simt(a, w, bias)[3 if M > 3 else 0])
+
+
+def paged_case(K, dtype, n_heads, kv_heads, d, page, lengths, new, window, n_splits, seed=0, poison=True, spike=None):
+    """Requests with `lengths` tokens of which the last `new` are this step's queries."""
+    g = torch.Generator().manual_seed(seed)
+    max_blocks = (max(lengths) + page - 1) // page + 1
+    n_pages = sum((L + page - 1) // page for L in lengths) + 5
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    cache = torch.full((n_pages, 2, kv_heads, page, d), float("nan") if poison else 0.0).to(dtype).to(DEV)
+    table = torch.full((len(lengths), max_blocks), -1, dtype=torch.int32)
+    qs, ks, vs, ent, pos = [], [], [], [], []
+    refs = []
+    scale = d ** -0.5
+    for e, (L, n) in enumerate(zip(lengths, new)):
+        q = torch.randn(L, n_heads, d, generator=g)
+        k = torch.randn(L, kv_heads, d, generator=g)
+        v = torch.randn(L, kv_heads, d, generator=g)
+        if spike is not None and L > spike + 1:
+            # one far key stands out for the last query
+            k[spike] *= 0; k[spike, :, 0] = 30.0
+            q[L - 1] *= 0; q[L - 1, :, 0] = 30.0
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        for b in range((L + page - 1) // page):
+            table[e, b] = perm.pop()
+        # earlier tokens are already in the cache
+        for j in range(L - n):
+            pg = table[e, j // page]
+            cache[pg, 0, :, j % page] = k[j].to(DEV)
+            cache[pg, 1, :, j % page] = v[j].to(DEV)
+        qs.append(q[L - n:]); ks.append(k[L - n:]); vs.append(v[L - n:])
+        ent += [e] * n; pos += list(range(L - n, L))
+        rep = n_heads // kv_heads
+        kk, vv = k.double().repeat_interleave(rep, 1), v.double().repeat_interleave(rep, 1)
+        s = torch.einsum("ihd,jhd->hij", q.double(), kk) * scale
+        i, j = torch.arange(L)[:, None], torch.arange(L)[None, :]
+        vis = j <= i
+        if window:
+            vis = vis & (j > i - window)
+        s = s.masked_fill(~vis, float("-inf"))
+        refs.append(torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), vv)[L - n:].reshape(n, n_heads * d))
+    q = torch.cat(qs).reshape(-1, n_heads * d).to(DEV)
+    k = torch.cat(ks).reshape(-1, kv_heads * d).to(DEV)
+    v = torch.cat(vs).reshape(-1, kv_heads * d).to(DEV)
+    # the three live side by side in one buffer, as after a fused QKV projection
+    packed = torch.cat([q, k, v], 1).contiguous()
+    qv, kv_, vv_ = packed[:, :n_heads * d], packed[:, n_heads * d:(n_heads + kv_heads) * d], packed[:, (n_heads + kv_heads) * d:]
+    ent = torch.tensor(ent, dtype=torch.int32, device=DEV)
+    pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    table = table.to(DEV)
+    K.kv_store(kv_, vv_, ent, pos, table, cache)
+    return dict(q=qv, cache=cache, ent=ent, pos=pos, table=table, ref=torch.cat(refs), scale=scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(6, 2, 48, 8), (5, 5, 16, 16), (3, 1, 128, 4), (2, 2, 200, 16)])
+@pytest.mark.parametrize("window", [None, 7])
+def test_attention_rows_mixed(K, dtype, heads, kv_heads, d, page, window):
+    c = paged_case(K, dtype, heads, kv_heads, d, page, lengths=[37, 1, 90, 64], new=[37, 1, 2, 1], window=window, n_splits=1)
+    out = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window)
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_splits", [2, 5, 32])
+def test_attention_rows_split_decode(K, dtype, n_splits):
+    c = paged_case(K, dtype, 4, 2, 64, 16, lengths=[300, 33, 1, 700], new=[1, 1, 1, 1], window=None, n_splits=n_splits,
+                   spike=5)
+    out = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], 4, c["scale"], None, n_splits=n_splits)
+    assert K.read_error_flag(DEV) == 0
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(dtype)
+    one = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], 4, c["scale"], None, n_splits=1)
+    assert (out.float() - one.float()).abs().max() < tol(dtype)
+
+
+def test_attention_rejects_bad_sizes(K):
+    cache = torch.zeros(4, 2, 2, 16, 20, device=DEV)
+    q = torch.zeros(1, 40, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(K.KernelError, match="head size"):
+        K.attention_rows(q, cache, z, z, torch.zeros(1, 2, dtype=torch.int32, device=DEV), 2, 1.0)
+    with pytest.raises(K.KernelError, match="no CPU fallback"):
+        K.layernorm(torch.zeros(2, 8), torch.zeros(8), None, 1e-5, torch.float32)
+
+
+def test_attention_missing_page_sets_flag(K):
+    c = paged_case(K, torch.float32, 2, 2, 16, 8, lengths=[20], new=[1], window=None, n_splits=1, poison=False)
+    c["table"][0, 1] = -1
+    K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], 2, c["scale"])
+    assert K.read_error_flag(DEV) == 4
+
+
+def test_sampling(K):
+    import sys
+    from plain_gpt2 import sample_token
+    g = torch.Generator().manual_seed(5)
+    V = 1003
+    logits = (torch.randn(6, V, generator=g) * 3)
+    logits[1, 17] = logits[1, 400] = 50.0           # a tie: the first index wins
+    logits[2, 5] = float("nan")
+    logits[3, :] = float("-inf")
+    logits[4, 9] = float("inf")
+    dev = logits.to(DEV)
+    greedy = K.sample(dev).cpu().tolist()
+    assert greedy[0] == int(logits[0].argmax()) and greedy[1] == 17 and greedy[2:5] == [-1, -1, -1]
+    assert greedy[5] == int(logits[5].argmax())
+    rows = torch.randn(64, V, generator=g) * 2
+    temps = torch.tensor([0.0, 0.8, 1.0, 1.7] * 16)
+    us = torch.rand(64, generator=g, dtype=torch.float64)
+    us[1], us[2] = 0.0, 1.0 - 2 ** -53
+    got = K.sample(rows.to(DEV), temps.to(DEV), us.to(DEV)).cpu().tolist()
+    for r in range(64):
+        want = sample_token(rows[r], float(temps[r]), float(us[r]))
+        if got[r] != want:
+            # only a draw within rounding of a boundary of the CDF may differ, and then by one neighbour
+            z = torch.softmax(rows[r].double() / float(temps[r]), 0).cumsum(0)
+            assert abs(got[r] - want) == 1 and (z[min(got[r], want)] - float(us[r])).abs() < 1e-6
+    # a padded row stride is honoured
+    wide = torch.zeros(3, V + 13); wide[:, :V] = rows[:3]; wide[:, V:] = 100.0
+    assert K.sample(wide.to(DEV)[:, :V]).cpu().tolist() == [int(rows[i].argmax()) for i in range(3)]

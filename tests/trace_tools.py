@@ -62,3 +62,77 @@ class TraceBuilder:
             for (request, position), row in zip(self.where[number], rows):
                 got.setdefault(request, {})[position] = row
         return got
+
+
+def round64(n):
+    return (n + 63) // 64 * 64
+
+
+def whole_steps(requests):
+    """Each request alone and whole, every position wanted."""
+    b = TraceBuilder()
+    for r, tokens in requests.items():
+        b.step([(r, tokens, True)], end=[r])
+    return b
+
+
+def tail_steps(requests, tail=32):
+    """Most of a request in one step, its last `tail` tokens one by one."""
+    b = TraceBuilder()
+    for r, tokens in requests.items():
+        head = max(1, len(tokens) - tail)
+        b.step([(r, tokens[:head], True)])
+        for i in range(head, len(tokens)):
+            b.step([(r, tokens[i:i + 1], True)], end=[r] if i == len(tokens) - 1 else [])
+        if head == len(tokens):
+            b.step([], end=[r])
+    return b
+
+
+def portion_steps(requests, sizes=(7, 2, 16, 3, 2, 33, 5, 2, 64, 1)):
+    """Portions of changing size, down to two tokens (and one)."""
+    b = TraceBuilder()
+    for r, tokens in requests.items():
+        at, i = 0, 0
+        while at < len(tokens):
+            n = min(sizes[i % len(sizes)], len(tokens) - at)
+            b.step([(r, tokens[at:at + n], True)], end=[r] if at + n == len(tokens) else [])
+            at, i = at + n, i + 1
+    return b
+
+
+def mixed_steps(requests, seed=0, max_live=4, prompt_share=0.6):
+    """Up to max_live requests at a time: portions of some beside decoded tokens of others,
+    requests now and then left out of a step. Returns (builder, most tokens held at once, each
+    request's count rounded up to 64)."""
+    import random
+    rng = random.Random(seed)
+    b = TraceBuilder()
+    waiting = list(requests)
+    live, at = [], {}
+    peak = 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            r = waiting.pop(0)
+            live.append(r)
+            at[r] = 0
+        parts, ended = [], []
+        for r in list(live):
+            tokens = requests[r]
+            if len(live) > 1 and rng.random() < 0.15:
+                continue
+            left = len(tokens) - at[r]
+            if at[r] < int(prompt_share * len(tokens)):
+                n = min(left, rng.choice((2, 3, 5, 8, 13, 17, 32)))
+            else:
+                n = 1
+            parts.append((r, tokens[at[r]:at[r] + n], True))
+            at[r] += n
+            if at[r] == len(tokens):
+                ended.append(r)
+        peak = max(peak, sum(round64(at[r]) for r in live))
+        if parts:
+            b.step(parts, end=ended)
+        for r in ended:
+            live.remove(r)
+    return b, peak
