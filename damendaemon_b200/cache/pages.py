@@ -84,7 +84,7 @@ class PagePool:
         for p in pages:
             self._owner[p] = None
             self._free.append(p)
-        self._held[owner] -= len(pages)
+        self._held[owner] = self._held.get(owner, 0) - len(pages)
 
     def forget(self, owner):
         """Drop owner's promise; it must hold no pages any more."""

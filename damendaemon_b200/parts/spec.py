@@ -82,6 +82,10 @@ class LayerSpec:
     norm1: object
     norm2: object
 
+    @property
+    def kind(self):
+        return self.arrangement
+
 
 @dataclass(frozen=True)
 class RunEntry:
