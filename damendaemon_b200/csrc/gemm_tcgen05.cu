@@ -1,0 +1,321 @@
+// bfloat16 GEMM on the 5th-generation tensor cores: out[M,N] = act(X[M,K] . W[N,K]^T + bias) (+ residual).
+//
+// The product is computed transposed, D^T = W . X^T: the weight rows (output features)
+// are the 128-row M side of tcgen05.mma and the tokens its N side (16..256), so the same
+// kernel serves a decode step of a few tokens (narrow N tile, split over K to fill the
+// SMs while the weights stream from HBM once) and a prompt portion of thousands (N tile
+// 256). In TMEM the accumulator has one output feature per lane and one token per
+// column; an epilogue thread therefore owns one feature, its bias is one register, and a
+// warp's 32 lanes write 32 consecutive features of a token row: coalesced stores with no
+// staging through shared memory.
+//
+// Pipeline per CTA: warp 0 issues TMA loads (W tile 128x64 and X tile BNx64 bf16, 128-byte
+// swizzle) into a ring of stages guarded by full/empty mbarriers; warp 1 allocates TMEM
+// and issues tcgen05.mma from shared-memory descriptors, releasing stages with
+// tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld and apply the epilogue.
+// With split-K each CTA writes its float32 partial tile to a workspace; the CTA that
+// arrives last at the tile's counter sums the partials in split order (deterministic) and
+// applies the epilogue, then resets the counter for the next launch.
+//
+// Every mbarrier wait is bounded (tcgen05.cuh); on a timeout the kernel sets bit 8 of the
+// error word, stops waiting everywhere, frees its TMEM and returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // output features per tile (tcgen05.mma M)
+constexpr int BK = 64;           // k elements per stage: one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;     // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+
+struct GemmParams {
+    const float* bias;           // [N] or null
+    const float* residual;       // [M, ldr] or null
+    void* out;                   // [M, ldo] bf16 or f32
+    float* workspace;            // [splits, M, N] f32 (split-K only)
+    int* counters;               // one per output tile, zero between launches (split-K only)
+    int* error_flag;
+    int M, N, K;                 // tokens, output features, reduction
+    int ldr, ldo;
+    int act, out_dtype;
+    int splits, kblocks_per_split;
+};
+
+template <int BN> struct Config {
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void store_out(const GemmParams& p, int m, int n, float v) {
+    if (p.bias) v += p.bias[n];
+    v = dd_activation(v, p.act);
+    if (p.residual) v += p.residual[(size_t)m * p.ldr + n];
+    if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmParams p) {
+    using C = Config<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // the swizzled tiles need 1024-byte alignment
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + C::STAGES;
+    uint64_t* tmem_full_bar = empty_bar + C::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;            // first output feature of the tile
+    const int m0 = blockIdx.y * BN;            // first token of the tile
+    const int split = blockIdx.z;
+    const int total_kblocks = (p.K + BK - 1) / BK;
+    const int kb_begin = split * p.kblocks_per_split;
+    const int kb_end = min(total_kblocks, kb_begin + p.kblocks_per_split);
+    const int n_kblocks = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        tc::mbar_init(tmem_full_bar, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::prefetch_tensormap(&map_w);
+            tc::prefetch_tensormap(&map_x);
+            for (int i = 0; i < n_kblocks; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t phase = (i / C::STAGES) & 1;
+                if (!tc::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) break;
+                uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
+                uint8_t* b_dst = a_dst + C::A_BYTES;
+                tc::mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+                tc::tma_load_2d(a_dst, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+                tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kblocks && ok; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t phase = (i / C::STAGES) & 1;
+                ok = tc::mbar_wait(&full_bar[s], phase, abort_flag);
+                if (!ok) break;
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles + s * C::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = tc::smem_desc_sw128(a_addr + k * UMMA_K * 2);
+                    const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
+                    tc::mma_bf16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::mma_commit(&empty_bar[s]);     // the stage is free once these MMAs have read it
+            }
+            tc::mma_commit(tmem_full_bar);         // the accumulator is complete
+        }
+    } else {
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. 32*(w%4)+31
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;
+        const bool n_ok = n < p.N;
+        const bool waited = n_kblocks == 0 ? true : tc::mbar_wait(tmem_full_bar, 0, abort_flag);
+        tc::fence_after_sync();
+        const bool have_acc = waited && n_kblocks > 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (p.splits == 1) {
+            if (waited) {
+                for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                    uint32_t r[16];
+                    if (have_acc) { tc::tmem_ld_x16(lane_addr + c0, r); tc::tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = 0;
+                    }
+                    if (n_ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (m < p.M) store_out(p, m, n, __uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        } else {
+            // partial sums to the workspace, then the last CTA of this tile reduces
+            float* ws = p.workspace + (size_t)split * p.M * p.N;
+            for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                uint32_t r[16];
+                if (have_acc) { tc::tmem_ld_x16(lane_addr + c0, r); tc::tmem_ld_wait(); }
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0;
+                }
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (m < p.M) ws[(size_t)m * p.N + n] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            if (warp == 2 && lane == 0) {
+                const int prev = atomicAdd(&p.counters[tile], 1);
+                *last_flag = (prev == p.splits - 1) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag) {
+                __threadfence();
+                if (n_ok && !*abort_flag) {
+                    for (int m = m0; m < min(p.M, m0 + BN); ++m) {
+                        float v = 0.f;
+                        for (int s = 0; s < p.splits; ++s)
+                            v += __ldcg(p.workspace + ((size_t)s * p.M + m) * p.N + n);
+                        store_out(p, m, n, v);
+                    }
+                }
+                if (warp == 2 && lane == 0) p.counters[tile] = 0;
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 8);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+// rows x K bf16 matrix with row stride ld elements; boxes of box_rows x 64, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows, const char* what) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return dd_fail("dd_gemm_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return dd_fail("dd_gemm_tcgen05: cannot describe %s to TMA (driver error %d)", what, (int)r);
+    return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t s) {
+    using C = Config<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(dd_ceil_div(p.N, BM), dd_ceil_div(p.M, BN), p.splits);
+    gemm_tcgen05_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, s>>>(mw, mx, p);
+    return dd_check_launch("dd_gemm_tcgen05");
+}
+
+}  // namespace
+
+// Chooses the token tile and the K split for a problem; also tells the caller how much workspace it needs.
+// Returns splits (>= 1); *token_tile gets BN.
+DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile) {
+    int bn = 256;
+    if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64; else if (M <= 128) bn = 128;
+    if (token_tile) *token_tile = bn;
+    const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
+    const int kblocks = dd_ceil_div(K, BK);
+    int splits = 1;
+    if (tiles * 3 < sm_count * 2) {
+        splits = dd_ceil_div(sm_count, tiles);
+        if (splits > kblocks / 2) splits = kblocks / 2;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    return splits;
+}
+
+// X [M,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw); bias [N] f32 or null; residual [M,N] f32
+// (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). workspace: f32
+// [splits*M*N] and counters: int32 [tiles], zero before the first launch (both only when splits > 1).
+DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const float* bias, const float* residual,
+                           int ldr, void* out, int ldo, int M, int N, int K, int act, int out_dtype, int splits,
+                           int token_tile, float* workspace, int* counters, int n_counters, int* error_flag,
+                           void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
+        return dd_fail("dd_gemm_tcgen05: K=%d and the row strides (%d, %d) must be multiples of 8 (TMA needs 16-byte rows)", K, ldx, ldw);
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return dd_fail("dd_gemm_tcgen05: operands must be 16-byte aligned");
+    if (out_dtype != DD_BF16 && out_dtype != DD_F32) return dd_fail("dd_gemm_tcgen05: unknown output dtype %d", out_dtype);
+    const int kblocks = dd_ceil_div(K, BK);
+    if (splits < 1 || splits > kblocks) return dd_fail("dd_gemm_tcgen05: bad split count %d for %d k-blocks", splits, kblocks);
+    GemmParams p;
+    p.bias = bias; p.residual = residual; p.out = out; p.workspace = workspace; p.counters = counters;
+    p.error_flag = error_flag; p.M = M; p.N = N; p.K = K; p.ldr = ldr; p.ldo = ldo; p.act = act; p.out_dtype = out_dtype;
+    p.splits = splits; p.kblocks_per_split = dd_ceil_div(kblocks, splits);
+    p.splits = dd_ceil_div(kblocks, p.kblocks_per_split);     // no empty split
+    if (p.splits > 1) {
+        const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, token_tile);
+        if (!workspace || !counters || n_counters < tiles)
+            return dd_fail("dd_gemm_tcgen05: split-K needs a workspace and %d counters", tiles);
+    }
+    CUtensorMap mw, mx;
+    if (int e = make_map(&mw, W, N, K, ldw, BM, "the weight matrix")) return e;
+    if (int e = make_map(&mx, X, M, K, ldx, token_tile, "the activations")) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (token_tile) {
+        case 16: return launch<16>(mw, mx, p, s);
+        case 32: return launch<32>(mw, mx, p, s);
+        case 64: return launch<64>(mw, mx, p, s);
+        case 128: return launch<128>(mw, mx, p, s);
+        case 256: return launch<256>(mw, mx, p, s);
+    }
+    return dd_fail("dd_gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", token_tile);
+}

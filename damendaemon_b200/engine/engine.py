@@ -48,7 +48,7 @@ def require_cuda(device):
 
 class Engine:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", kv_tokens=None,
-                 page_size=16, max_requests=64, device="cuda:0", gemm="simt", check_device_errors=True):
+                 page_size=16, max_requests=64, device="cuda:0", gemm="auto", check_device_errors=True):
         """Either ``model_dir`` (config.json + model.safetensors) or ``config`` (the raw
         config.json dict) with ``tensors`` ({checkpoint name: tensor})."""
         self.device = require_cuda(device)

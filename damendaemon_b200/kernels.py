@@ -34,7 +34,11 @@ _SIGNATURES = {
                              + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void],
         "dd_sample": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
     },
-    "tensor": {},
+    "tensor": {
+        "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 7
+                           + [_c_void, _c_void, _c_int, _c_void, _c_void],
+    },
 }
 
 _libs, _lock = {}, threading.Lock()
@@ -212,4 +216,53 @@ def sample(logits, temperature=None, uniform=None, out=None):
     _call(library("core"), "dd_sample", _ptr(logits, "logits", torch.float32), logits.stride(0), rows, vocab,
           _ptr(temperature, "temperature", torch.float32), _ptr(uniform, "uniform", torch.float64),
           _ptr(out, "out", torch.int32), _stream())
+    return out
+
+
+_counters = {}
+_sm_count = {}
+
+
+def _tile_counters(device, n):
+    key = torch.device(device).index or 0
+    if key not in _counters or _counters[key].numel() < n:
+        _counters[key] = torch.zeros(max(n, 8192), dtype=torch.int32, device=device)
+    return _counters[key]
+
+
+def sm_count(device):
+    key = torch.device(device).index or 0
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_count[key]
+
+
+def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None, splits=None, token_tile=None):
+    """act(a @ w.T + bias) (+ residual) on the tcgen05 tensor cores. a [M,K] and w [N,K] bfloat16,
+    bias/residual float32, out bfloat16 or float32. K and the row strides must be multiples of 8."""
+    _rows(a, "a"), _rows(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError(f"gemm_tcgen05: needs bfloat16 a [M,K] and w [N,K]; got {tuple(a.shape)} {a.dtype}, {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _rows(out, "out")
+    lib = library("tensor")
+    tile = ctypes.c_int(0)
+    planned = lib.dd_gemm_tcgen05_plan(M, N, K, sm_count(a.device), ctypes.byref(tile))
+    splits = planned if splits is None else splits
+    token_tile = tile.value if token_tile is None else token_tile
+    workspace = counters = None
+    n_counters = 0
+    if splits > 1:
+        workspace = torch.empty((splits * M * N,), dtype=torch.float32, device=a.device)
+        n_counters = ((N + 127) // 128) * ((M + token_tile - 1) // token_tile)
+        counters = _tile_counters(a.device, n_counters)
+    _call(lib, "dd_gemm_tcgen05", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(0),
+          _ptr(bias, "bias", torch.float32), _ptr(residual, "residual", torch.float32),
+          0 if residual is None else residual.stride(0), _ptr(out, "out", out_dtype), out.stride(0), M, N, K,
+          ACTIVATIONS[activation], _dt(out_dtype), splits, token_tile, _ptr(workspace), _ptr(counters), n_counters,
+          _ptr(error_flag(a.device)), _stream())
     return out

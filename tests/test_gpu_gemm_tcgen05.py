@@ -1,0 +1,80 @@
+"""The tcgen05/TMA GEMM alone against a float64 product of the same bfloat16 operands."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from damendaemon_b200 import kernels
+    kernels.library("tensor")
+    return kernels
+
+
+def operands(M, N, Kd, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
+    return a, w, torch.randn(N, generator=g).to(DEV), torch.randn(M, N, generator=g).to(DEV)
+
+
+# (tokens, features, reduction): tile edges, k tails, widths and vocabularies that are no power of two
+SHAPES = [(1, 128, 64), (5, 200, 96), (16, 130, 320), (17, 1000, 96), (33, 96, 64), (64, 4800, 1600), (100, 1600, 6400),
+          (129, 515, 200), (300, 257, 1608), (8, 50257, 1600), (2048, 1600, 1600)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_plain_product(K, shape):
+    M, N, Kd = shape
+    a, w, bias, res = operands(M, N, Kd)
+    out = K.gemm_tcgen05(a, w, out_dtype=torch.float32)
+    assert K.read_error_flag(DEV) == 0
+    ref = a.double() @ w.double().t()
+    err = (out.double() - ref).abs().max().item()
+    assert err < 2e-4 * math.sqrt(Kd / 64), f"{shape}: {err}"          # float32 accumulation of exact bf16 products
+
+
+@pytest.mark.parametrize("shape", [(7, 300, 192), (64, 1600, 6400), (200, 6400, 1600), (1, 4800, 1600)])
+def test_epilogues(K, shape):
+    M, N, Kd = shape
+    a, w, bias, res = operands(M, N, Kd, seed=1)
+    base = a.double() @ w.double().t() + bias.double()
+    gelu_new = 0.5 * base * (1 + torch.tanh(math.sqrt(2 / math.pi) * (base + 0.044715 * base ** 3)))
+    gelu_erf = 0.5 * base * (1 + torch.erf(base / math.sqrt(2)))
+    rel = lambda ref: 2.0 ** -8 * float(ref.abs().max()) + 1e-3
+    out = K.gemm_tcgen05(a, w, bias)
+    assert out.dtype == torch.bfloat16 and (out.double() - base).abs().max() < rel(base)
+    assert (K.gemm_tcgen05(a, w, bias, activation="gelu_new").double() - gelu_new).abs().max() < rel(gelu_new)
+    assert (K.gemm_tcgen05(a, w, bias, activation="gelu").double() - gelu_erf).abs().max() < rel(gelu_erf)
+    stream = res.clone()
+    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream)
+    assert (stream.double() - (base + res.double())).abs().max() < 5e-4 * math.sqrt(Kd / 64)
+    assert K.read_error_flag(DEV) == 0
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 13])
+@pytest.mark.parametrize("tile", [16, 64, 256])
+def test_forced_splits_and_tiles(K, splits, tile):
+    a, w, bias, res = operands(40, 700, 1600, seed=2)
+    ref = a.double() @ w.double().t() + bias.double()
+    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile)
+    again = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile)
+    assert K.read_error_flag(DEV) == 0
+    assert (out.double() - ref).abs().max() < 1e-3
+    assert torch.equal(out, again), "split-K sums in a fixed order: two runs are bit-equal"
+
+
+def test_strided_views_and_refusals(K):
+    a, w, bias, res = operands(20, 256, 128, seed=3)
+    wide = torch.zeros(20, 128 + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, 64:] = a
+    out = K.gemm_tcgen05(wide[:, 64:], w, out_dtype=torch.float32)
+    assert torch.equal(out, K.gemm_tcgen05(a, w, out_dtype=torch.float32))
+    with pytest.raises(K.KernelError, match="multiples of 8"):
+        K.gemm_tcgen05(a[:, :100].contiguous(), w[:, :100].contiguous())
+    with pytest.raises(K.KernelError, match="bfloat16"):
+        K.gemm_tcgen05(a.float(), w.float())
