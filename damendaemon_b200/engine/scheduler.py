@@ -1,0 +1,245 @@
+"""The scheduler above the step function: admits requests, cuts prompts into portions under
+a token budget, decodes, finishes and frees.
+
+Decisions (the reference's, where it has them):
+* Admission is first-come first-served. A request is admitted when a request slot is free
+  and the cache can promise pages for its prompt plus max_tokens; if it cannot, the request
+  waits at the head of the queue and nothing behind it overtakes (damendaemon/scheduler.py:763-780).
+  A request that could never fit the whole pool fails at once (damendaemon/paged.py:47-48).
+  So an admitted request never runs out of pages in the middle of decoding; nothing is ever
+  evicted or swapped (the reference has no preemption either).
+* Without reservations (``reserve=False``) pages are claimed step by step. When a step does not
+  fit, the youngest admitted requests are left out of it until it does; if not even the oldest
+  request can take its next token, the youngest live request fails with 'cache_full' and its
+  pages go back, so the others can go on.
+* Every step holds all decoding requests (one token each) and fills the rest of the token
+  budget with prompt portions of the admitted requests in admission order, each at most
+  ``chunk_size`` tokens: one call of the step function, where the reference runs at most one
+  chunk of one request and then a separate decode batch (damendaemon/scheduler.py:680-722,827-873).
+* prompt + max_tokens must fit the context (damendaemon/prompts.py:4-9); with
+  ``length_policy='clamp'`` max_tokens is cut to what fits instead.
+* A request ends on an end-of-sequence token (unless ignore_eos), at max_tokens ('length'),
+  or at the model's last position. Its pages are given back before its last event is handed
+  out (damendaemon/scheduler.py:869-873).
+* A step that raises fails the requests in it and gives back their pages; the others go on
+  (damendaemon/scheduler.py:812-818,881-895).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Hashable, Optional
+
+from ..cache import PageCapacityError
+from ..sampling import Sampler, Sampling
+from .engine import StepEntry
+
+_ids = itertools.count()
+
+
+@dataclass
+class Request:
+    prompt: list
+    max_tokens: int = 128
+    sampling: Sampling = field(default_factory=Sampling)
+    ignore_eos: bool = False
+    id: Hashable = None
+    # filled in by the scheduler
+    output: list = field(default_factory=list)
+    fed: int = 0
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+    sampler: Optional[Sampler] = None
+    submitted_at: float = 0.0
+    first_token_at: Optional[float] = None
+    finished_at: Optional[float] = None
+
+    def __post_init__(self):
+        if self.id is None:
+            self.id = f"request-{next(_ids)}"
+
+    @property
+    def finished(self):
+        return self.finish_reason is not None
+
+
+@dataclass
+class TokenEvent:
+    request: Request
+    token: Optional[int]      # None for a request that ended without a token (an error)
+    finished: bool
+
+
+class Scheduler:
+    def __init__(self, engine, *, token_budget=2048, chunk_size=0, max_live=None, reserve=True,
+                 length_policy="reject", sample_fn=None):
+        if token_budget <= 0:
+            raise ValueError("token_budget must be positive")
+        if chunk_size < 0:
+            raise ValueError("chunk_size must be 0 (no limit below the budget) or positive")
+        if length_policy not in ("reject", "clamp"):
+            raise ValueError("length_policy must be 'reject' or 'clamp'")
+        self.engine = engine
+        self.token_budget = token_budget
+        self.chunk_size = chunk_size or token_budget
+        self.max_live = min(max_live or engine.cache.max_requests, engine.cache.max_requests)
+        self.reserve = reserve
+        self.length_policy = length_policy
+        if sample_fn is None:
+            from ..sampling import sample_rows as sample_fn
+        self.sample_fn = sample_fn
+        self.waiting = deque()
+        self.prefilling = []     # admitted, prompt not yet wholly in the cache; admission order
+        self.decoding = []       # admitted, generating; admission order
+        self.done = []
+        self.steps = 0
+        self.step_log = []       # (prompt tokens, decode tokens) of each step
+
+    # ------------------------------------------------------------------ intake
+    def submit(self, request: Request) -> Request:
+        context, vocab = self.engine.max_context, self.engine.spec.vocab_size
+        if not isinstance(request.prompt, list) or not request.prompt or \
+                any(type(t) is not int or not 0 <= t < vocab for t in request.prompt):
+            raise ValueError("prompt must be a nonempty list of token ids inside the vocabulary")
+        if type(request.max_tokens) is not int or request.max_tokens <= 0:
+            raise ValueError("max_tokens must be a positive integer")
+        if len(request.prompt) + request.max_tokens > context:
+            if self.length_policy == "reject" or len(request.prompt) >= context:
+                raise ValueError("prompt plus max_tokens exceeds configured context")
+            request.max_tokens = context - len(request.prompt)
+        request.sampler = Sampler(request.sampling)
+        request.sampler.prepare(request.prompt, vocab)
+        request.submitted_at = time.perf_counter()
+        self.waiting.append(request)
+        return request
+
+    @property
+    def idle(self):
+        return not (self.waiting or self.prefilling or self.decoding)
+
+    def live(self):
+        return self.prefilling + self.decoding
+
+    # ------------------------------------------------------------------ decisions
+    def _admit(self, events):
+        while self.waiting and len(self.live()) < self.max_live:
+            request = self.waiting[0]
+            total = len(request.prompt) + request.max_tokens
+            try:
+                if self.reserve:
+                    self.engine.reserve(request.id, total, min(self.chunk_size, self.token_budget))
+                else:
+                    self.engine.cache.admit(request.id)
+            except PageCapacityError:
+                break                                   # wait at the head of the queue; nobody overtakes
+            except ValueError as error:                 # can never fit
+                self.waiting.popleft()
+                self._fail(request, str(error), events, release=False)
+                continue
+            self.waiting.popleft()
+            self.prefilling.append(request)
+
+    def plan(self):
+        """The next step's entries as (request, tokens, want), decided from host state only."""
+        entries, budget = [], self.token_budget
+        for request in self.decoding:
+            entries.append((request, [request.output[-1]], [0]))
+            budget -= 1
+        for request in self.prefilling:
+            if budget <= 0:
+                break
+            n = min(len(request.prompt) - request.fed, self.chunk_size, budget)
+            final = request.fed + n == len(request.prompt)
+            entries.append((request, request.prompt[request.fed:request.fed + n], [n - 1] if final else []))
+            budget -= n
+        if not self.reserve:
+            entries = self._fit(entries)
+        return entries
+
+    def _fit(self, entries):
+        """Leave out the youngest requests until the cache can take the step."""
+        cache = self.engine.cache
+        order = {r.id: i for i, r in enumerate(sorted(self.live(), key=lambda r: r.submitted_at))}
+        kept = sorted(entries, key=lambda e: order[e[0].id])
+        while kept and not cache.can_extend([(r.id, cache.length[r.id] + len(t)) for r, t, _ in kept]):
+            kept.pop()
+        return [e for e in entries if any(e[0] is k[0] for k in kept)]
+
+    # ------------------------------------------------------------------ one step
+    def step(self):
+        """Admit, run one step of the engine, sample, finish. Returns the step's TokenEvents."""
+        events = []
+        self._admit(events)
+        entries = self.plan()
+        if not entries:
+            if not self.reserve and self.live():
+                youngest = max(self.live(), key=lambda r: r.submitted_at)
+                self._fail(youngest, "cache_full", events)
+            return events
+        try:
+            logits = self.engine.step([StepEntry(r.id, tokens, want) for r, tokens, want in entries])
+            rows = [r for r, _, want in entries if want]
+            tokens = self.sample_fn(logits, [r.sampler for r in rows]) if rows else []
+        except Exception as error:      # the step failed: its requests fail, the others go on
+            for request, _, _ in entries:
+                self._fail(request, f"{type(error).__name__}: {error}", events)
+            return events
+        self.steps += 1
+        self.step_log.append((sum(len(t) for r, t, _ in entries if r in self.prefilling),
+                              sum(1 for r, _, _ in entries if r in self.decoding)))
+        now = time.perf_counter()
+        for request, fed_tokens, _ in entries:
+            if request in self.prefilling:
+                request.fed += len(fed_tokens)
+        for request, token in zip(rows, tokens):
+            if request in self.prefilling:
+                self.prefilling.remove(request)
+                self.decoding.append(request)
+                request.first_token_at = now
+            request.output.append(token)
+            request.sampler.observe(token)
+            reason = None
+            if not request.ignore_eos and token in self.engine.spec.eos_token_ids:
+                reason = "stop"
+            elif len(request.output) >= request.max_tokens:
+                reason = "length"
+            elif len(request.prompt) + len(request.output) >= self.engine.max_context:
+                reason = "length"
+            if reason:
+                self._finish(request, reason)
+            events.append(TokenEvent(request, token, reason is not None))
+        return events
+
+    def _finish(self, request, reason):
+        self.engine.finish(request.id)                  # pages go back before the last event is seen
+        request.finish_reason = reason
+        request.finished_at = time.perf_counter()
+        for group in (self.prefilling, self.decoding):
+            if request in group:
+                group.remove(request)
+        self.done.append(request)
+
+    def _fail(self, request, message, events, release=True):
+        if release:
+            self.engine.finish(request.id)
+        request.finish_reason, request.error = "error", message
+        request.finished_at = time.perf_counter()
+        for group in (self.prefilling, self.decoding):
+            if request in group:
+                group.remove(request)
+        self.done.append(request)
+        events.append(TokenEvent(request, None, True))
+
+    def run(self):
+        """Step until every submitted request has ended; yields TokenEvents."""
+        while not self.idle:
+            events = self.step()
+            yield from events
+            if not events and not self.live() and self.waiting:
+                # nothing is live and the head of the queue still cannot be admitted: it never will be
+                request = self.waiting.popleft()
+                failed = []
+                self._fail(request, "cache pages do not suffice for this request", failed, release=False)
+                yield from failed

@@ -32,7 +32,8 @@ _SIGNATURES = {
         "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 6 + [_c_void, _c_void],
         "dd_attention_rows": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
                              + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void],
-        "dd_sample": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
+        "dd_sample": [_c_void, _c_int, _c_int, _c_int] + [_c_void] * 6,
+        "dd_adjust_logits": [_c_void, _c_int, _c_int] + [_c_void] * 8 + [_c_int, _c_void],
     },
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void],
@@ -204,9 +205,10 @@ def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale
     return out
 
 
-def sample(logits, temperature=None, uniform=None, out=None):
+def sample(logits, temperature=None, uniform=None, top_k=None, top_p=None, out=None):
     """Row-wise token choice: argmax where temperature is 0 (or None), else an inverse-CDF draw
-    with the given uniform numbers. Returns int32 ids, -1 for rows without a finite maximum."""
+    with the given uniform numbers over the tokens that top_k and top_p keep. Returns int32 ids,
+    -1 for rows without a finite maximum."""
     _rows(logits, "logits")
     rows, vocab = logits.shape
     if out is None:
@@ -214,9 +216,22 @@ def sample(logits, temperature=None, uniform=None, out=None):
     if temperature is not None and uniform is None:
         raise KernelError("sampling with a temperature needs uniform draws")
     _call(library("core"), "dd_sample", _ptr(logits, "logits", torch.float32), logits.stride(0), rows, vocab,
-          _ptr(temperature, "temperature", torch.float32), _ptr(uniform, "uniform", torch.float64),
+          _ptr(temperature, "temperature", torch.float32), _ptr(top_k, "top_k", torch.int32),
+          _ptr(top_p, "top_p", torch.float32), _ptr(uniform, "uniform", torch.float64),
           _ptr(out, "out", torch.int32), _stream())
     return out
+
+
+def adjust_logits(logits, item_row, item_token, item_count, item_bias, item_seen, repetition, frequency, presence):
+    """In place: penalties and bias on the listed (row, token) pairs (each pair listed once)."""
+    _rows(logits, "logits")
+    _call(library("core"), "dd_adjust_logits", _ptr(logits, "logits", torch.float32), logits.stride(0), logits.shape[1],
+          _ptr(item_row, "item_row", torch.int32), _ptr(item_token, "item_token", torch.int32),
+          _ptr(item_count, "item_count", torch.float32), _ptr(item_bias, "item_bias", torch.float32),
+          _ptr(item_seen, "item_seen", torch.int32), _ptr(repetition, "repetition", torch.float32),
+          _ptr(frequency, "frequency", torch.float32), _ptr(presence, "presence", torch.float32),
+          item_row.numel(), _stream())
+    return logits
 
 
 _counters = {}

@@ -1,0 +1,136 @@
+"""The scheduler's decisions, with a counting stand-in for the engine and the real cache manager."""
+import pytest
+
+from damendaemon_b200.engine.scheduler import Request, Scheduler
+from fake_engine import FakeEngine, greedy_cpu
+
+
+def make(engine=None, **kw):
+    engine = engine or FakeEngine()
+    return engine, Scheduler(engine, sample_fn=greedy_cpu, **kw)
+
+
+def drain(s):
+    return list(s.run())
+
+
+def test_one_request_counts_up_and_frees():
+    engine, s = make()
+    r = s.submit(Request([1, 2, 3], max_tokens=4, ignore_eos=True))
+    events = drain(s)
+    assert r.output == [4, 5, 6, 7] and r.finish_reason == "length"
+    assert [e.token for e in events] == [4, 5, 6, 7] and events[-1].finished
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+
+
+def test_eos_stops_unless_ignored():
+    engine, s = make()
+    a = s.submit(Request([7], max_tokens=10))
+    b = s.submit(Request([7], max_tokens=5, ignore_eos=True))
+    drain(s)
+    assert a.output == [8, 9] and a.finish_reason == "stop"
+    assert b.output == [8, 9, 10, 11, 12] and b.finish_reason == "length"
+
+
+def test_portions_under_a_token_budget_and_decodes_first():
+    engine, s = make(FakeEngine(kv_tokens=512, max_context=128), token_budget=16, chunk_size=10)
+    a = s.submit(Request(list(range(1, 4)), max_tokens=6, ignore_eos=True))
+    b = s.submit(Request(list(range(20, 45)), max_tokens=2, ignore_eos=True))
+    drain(s)
+    # step 0: a whole (3) and b's first 10; step 1: a decodes beside b's next 10; ...
+    assert engine.calls[0] == [(a.id, 3, [2]), (b.id, 10, [])]
+    assert engine.calls[1] == [(a.id, 1, [0]), (b.id, 10, [])]
+    assert engine.calls[2] == [(a.id, 1, [0]), (b.id, 5, [4])]
+    assert all(sum(n for _, n, _ in call) <= 16 for call in engine.calls)
+    assert b.output == [45, 46] and a.output == [4, 5, 6, 7, 8, 9]
+
+
+def test_budget_is_shared_in_admission_order():
+    engine, s = make(FakeEngine(kv_tokens=512), token_budget=8)
+    rs = [s.submit(Request(list(range(10, 16)), max_tokens=1, ignore_eos=True)) for _ in range(3)]
+    s.step()
+    assert engine.calls[0] == [(rs[0].id, 6, [5]), (rs[1].id, 2, [])]
+
+
+def test_queue_waits_for_pages_in_order_then_reuses_them():
+    # pool of 4 pages (64 tokens): each request reserves 3 pages
+    engine, s = make(FakeEngine(kv_tokens=64, max_requests=4), token_budget=64)
+    a = s.submit(Request([1] * 30, max_tokens=10, ignore_eos=True))
+    b = s.submit(Request([2] * 30, max_tokens=10, ignore_eos=True))
+    c = s.submit(Request([3], max_tokens=1, ignore_eos=True))        # small, but must not overtake b
+    s.step()
+    assert [r.id for r in s.live()] == [a.id] and list(s.waiting) == [b, c]
+    drain(s)
+    assert all(r.finish_reason == "length" for r in (a, b, c))
+    first_b = next(i for i, call in enumerate(engine.calls) if any(r == b.id for r, _, _ in call))
+    first_c = next(i for i, call in enumerate(engine.calls) if any(r == c.id for r, _, _ in call))
+    last_a = max(i for i, call in enumerate(engine.calls) if any(r == a.id for r, _, _ in call))
+    assert first_b > last_a and first_c >= first_b
+    assert engine.cache.used_tokens == 0
+
+
+def test_request_larger_than_the_pool_fails_at_once():
+    engine, s = make(FakeEngine(kv_tokens=32, max_context=128))
+    big = s.submit(Request([1] * 40, max_tokens=8))
+    small = s.submit(Request([1, 2], max_tokens=2, ignore_eos=True))
+    events = drain(s)
+    assert big.finish_reason == "error" and "pages" in big.error
+    assert small.output == [3, 4]
+    assert any(e.request is big and e.token is None and e.finished for e in events)
+
+
+def test_length_policy():
+    engine, s = make(FakeEngine(max_context=32, kv_tokens=64))
+    with pytest.raises(ValueError, match="exceeds"):
+        s.submit(Request([1] * 30, max_tokens=10))
+    engine, s = make(FakeEngine(max_context=32, kv_tokens=64), length_policy="clamp")
+    r = s.submit(Request([1] * 30, max_tokens=10, ignore_eos=True))
+    drain(s)
+    assert len(r.output) == 2 and r.finish_reason == "length"
+    for bad in (Request([], 1), Request([1000], 1), Request([1], 0), Request("ab", 1)):
+        with pytest.raises(ValueError):
+            s.submit(bad)
+
+
+def test_failed_step_fails_its_requests_and_frees_them():
+    engine, s = make(FakeEngine(kv_tokens=256))
+    a = s.submit(Request([1, 2], max_tokens=5, ignore_eos=True))
+    s.step()
+    engine.fail_next = RuntimeError("boom")
+    b = s.submit(Request([5], max_tokens=2, ignore_eos=True))
+    events = s.step()
+    assert a.finish_reason == b.finish_reason == "error" and "boom" in a.error
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+    c = s.submit(Request([5], max_tokens=2, ignore_eos=True))
+    drain(s)
+    assert c.output == [6, 7]
+
+
+def test_without_reservations_the_youngest_waits_and_at_worst_fails():
+    # 4 pages; two requests that together outgrow them while decoding
+    engine, s = make(FakeEngine(kv_tokens=64, max_context=64), reserve=False, token_budget=64)
+    a = s.submit(Request([1] * 30, max_tokens=30, ignore_eos=True))
+    b = s.submit(Request([2] * 30, max_tokens=30, ignore_eos=True))
+    drain(s)
+    assert a.finish_reason == "length" and len(a.output) == 30      # the oldest always gets through
+    assert b.finish_reason == "error" and b.error == "cache_full"
+    assert engine.cache.used_tokens == 0
+    engine.cache.check()
+
+
+def test_max_live_and_slots():
+    engine, s = make(FakeEngine(kv_tokens=1024, max_requests=2), max_live=8)
+    rs = [s.submit(Request([i + 1], max_tokens=3, ignore_eos=True)) for i in range(5)]
+    s.step()
+    assert len(s.live()) == 2
+    drain(s)
+    assert [r.output for r in rs] == [[i + 2, i + 3, i + 4] for i in range(5)]
+
+
+def test_window_group_gives_pages_back_while_running():
+    engine, s = make(FakeEngine(kv_tokens=128, max_context=128, window=20), token_budget=16)
+    r = s.submit(Request([1] * 100, max_tokens=20, ignore_eos=True))
+    drain(s)
+    full, window = engine.cache.groups
+    assert full.pool.high_water_pages == 8 and window.pool.high_water_pages <= 4
+    assert r.finish_reason == "length" and engine.cache.used_tokens == 0

@@ -1,0 +1,108 @@
+"""Weight loading by name: prefixes, ignored buffers, the tied head, and ONE error that lists
+everything that is wrong (mirrors the corruptions of the reference's
+tests/test_starcoder_cpu_reference.py and tests/test_floating_parameter.py:46-63)."""
+import json
+
+import pytest
+import torch
+
+from conftest import TINY_A, TINY_B
+from damendaemon_b200.parts import tensor_decls
+from damendaemon_b200.registry import architecture_of
+from damendaemon_b200.weights import (CheckpointFormatError, DictSource, SafetensorsFile, WeightError, check_and_place,
+                                      load_weights, write_random_model, write_safetensors)
+
+
+def setup(config):
+    arch = architecture_of(config)
+    typed = arch.parse_config(config)
+    spec = arch.build_spec(typed)
+    return arch, typed, spec, tensor_decls(spec)
+
+
+def test_random_folder_round_trip(tmp_path):
+    arch, typed, spec, decls = setup(TINY_B)
+    folder = write_random_model(tmp_path / "m", TINY_B, seed=1, dtype="bfloat16")
+    again = write_random_model(tmp_path / "n", TINY_B, seed=1, dtype="bfloat16")
+    assert (folder / "model.safetensors").read_bytes() == (again / "model.safetensors").read_bytes()
+    other = write_random_model(tmp_path / "o", TINY_B, seed=2, dtype="bfloat16")
+    assert (folder / "model.safetensors").read_bytes() != (other / "model.safetensors").read_bytes()
+    assert json.loads((folder / "config.json").read_text())["n_inner"] == 320
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        assert f.describe("wte.weight") == (torch.bfloat16, (1000, 96))
+        assert f.describe("h.0.ln_1.weight") == (torch.float32, (96,))
+        assert f.describe("h.2.mlp.c_fc.weight") == (torch.bfloat16, (96, 320))
+    for engine_dtype in (torch.bfloat16, torch.float32):
+        w = load_weights(folder, spec, decls, engine_dtype, "cpu")
+        assert w["h.1.attn.c_attn.weight"].shape == (288, 96) and w["h.1.attn.c_attn.weight"].dtype == engine_dtype
+        assert w["h.1.attn.c_attn.weight"].is_contiguous()
+        assert w["h.1.mlp.c_proj.weight"].shape == (96, 320)
+        assert w["h.1.attn.c_attn.bias"].dtype == torch.float32 and w["ln_f.weight"].dtype == torch.float32
+        assert w["wpe.weight"].dtype == engine_dtype
+    # the init scheme: c_proj matrices are narrower by sqrt(2 * n_layer)
+    t = arch.random_tensors(typed, 1)
+    assert t["h.0.attn.c_proj.weight"].std() < 0.6 * t["h.0.attn.c_attn.weight"].std()
+    assert abs(float(t["h.0.ln_1.weight"].mean()) - 1.0) < 0.02
+
+
+def test_prefix_buffers_and_tied_head():
+    arch, typed, spec, decls = setup(TINY_A)
+    t = arch.random_tensors(typed, 0)
+    plain = check_and_place(DictSource(t), spec, decls, torch.float32, "cpu")
+    prefixed = {"transformer." + k: v for k, v in t.items()}
+    prefixed["transformer.h.0.attn.bias"] = torch.ones(1, 1, 128, 128)
+    prefixed["transformer.h.1.attn.masked_bias"] = torch.tensor(-1e4)
+    prefixed["lm_head.weight"] = t["wte.weight"].clone()
+    placed = check_and_place(DictSource(prefixed), spec, decls, torch.float32, "cpu")
+    assert all(torch.equal(plain[k], placed[k]) for k in plain)
+    prefixed["lm_head.weight"] = t["wte.weight"] + 1
+    with pytest.raises(WeightError, match="tied"):
+        check_and_place(DictSource(prefixed), spec, decls, torch.float32, "cpu")
+
+
+def test_one_error_lists_everything():
+    arch, typed, spec, decls = setup(TINY_A)
+    t = arch.random_tensors(typed, 0)
+    del t["h.1.ln_2.bias"], t["wpe.weight"]
+    t["h.0.mlp.c_fc.weight"] = t["h.0.mlp.c_fc.weight"].t().contiguous()      # [out, in] instead of Conv1D's [in, out]
+    t["h.0.attn.c_proj.bias"] = torch.zeros(63)
+    t["h.0.extra.weight"] = torch.zeros(2)
+    t["ln_f.weight"] = torch.ones(64, dtype=torch.int8)
+    with pytest.raises(WeightError) as info:
+        check_and_place(DictSource(t), spec, decls, torch.float32, "cpu")
+    e = info.value
+    assert sorted(e.missing) == ["h.1.ln_2.bias", "wpe.weight"] and e.unexpected == ["h.0.extra.weight"]
+    assert len(e.wrong_shape) == 2 and len(e.wrong_dtype) == 1
+    text = str(e)
+    for piece in ("missing tensors (2)", "h.1.ln_2.bias", "unexpected tensors (1)", "h.0.extra.weight", "wrong shapes (2)",
+                  "expected (64, 256), found (256, 64)", "wrong dtypes (1)", "ln_f.weight"):
+        assert piece in text, piece
+
+
+def test_file_format_checks(tmp_path):
+    path = tmp_path / "model.safetensors"
+    write_safetensors(path, {"a": torch.arange(6, dtype=torch.float32).reshape(2, 3), "b": torch.zeros(0)})
+    with SafetensorsFile(path) as f:
+        assert f.tensor("a").tolist() == [[0, 1, 2], [3, 4, 5]] and f.tensor("b").numel() == 0
+    raw = path.read_bytes()
+    path.write_bytes(raw[:-4])
+    with pytest.raises(CheckpointFormatError):
+        SafetensorsFile(path)
+    path.write_bytes(b"\xff" * 8 + raw[8:])
+    with pytest.raises(CheckpointFormatError, match="header length"):
+        SafetensorsFile(path)
+    path.write_bytes(raw[:8] + raw[8:].replace(b'"a"', b'"b"', 1))
+    with pytest.raises(CheckpointFormatError, match="duplicate"):
+        SafetensorsFile(path)
+    with pytest.raises(WeightError, match="no model.safetensors"):
+        load_weights(tmp_path / "nowhere", None, [], torch.float32, "cpu")
+
+
+def test_engine_refuses_without_cuda(tmp_path):
+    if torch.cuda.is_available():
+        pytest.skip("needs a machine without CUDA")
+    from damendaemon_b200.engine import Engine
+    from damendaemon_b200.kernels import KernelError
+    folder = write_random_model(tmp_path / "m", TINY_A, 0)
+    with pytest.raises(KernelError, match="no CPU fallback"):
+        Engine(folder, dtype="float32")
