@@ -75,7 +75,8 @@ class CacheGroup:
 
 class CacheManager:
     def __init__(self, layer_needs, kv_tokens: int, page_size: int, max_requests: int, max_context: int):
-        """layer_needs: one list per model layer of PagedKeyValues / RequestState needs."""
+        """layer_needs: one list of PagedKeyValues / RequestState needs per cache site (a stop of the
+        model's run order; the "layers" of a group below are these indices)."""
         if type(page_size) is not int or page_size <= 0:
             raise ValueError("page size must be a positive integer")
         if type(kv_tokens) is not int or kv_tokens < page_size:
@@ -114,11 +115,12 @@ class CacheManager:
             self.state[layer] = torch.zeros((self.max_requests, *need.shape), device=device,
                                             dtype=getattr(torch, need.dtype))
 
-    def layer_view(self, layer):
-        """What a mixer sees of the cache: its group's arena slice and its state rows."""
+    def layer_view(self, layer, writable=True):
+        """What a mixer sees of the cache: its group's arena slice and its state rows.
+        ``layer`` counts the entries of ``layer_needs`` (the stops of the model's run order)."""
         g = self.group_of_layer.get(layer)
         return LayerCache(group=g, kv=None if g is None or g.arena is None else g.arena[g.layers.index(layer)],
-                          state=self.state.get(layer), page_size=self.page_size)
+                          state=self.state.get(layer), page_size=self.page_size, writable=writable)
 
     def bytes_per_token(self, element_size):
         return sum(len(g.layers) * 2 * g.need.kv_heads * g.need.head_dim * element_size for g in self.groups)
@@ -247,3 +249,4 @@ class LayerCache:
     kv: object
     state: object
     page_size: int
+    writable: bool = True      # False: this mixer reads another stop's cache and must not write it

@@ -48,7 +48,8 @@ def require_cuda(device):
 
 class Engine:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", kv_tokens=None,
-                 page_size=16, max_requests=64, device="cuda:0", gemm="auto", check_device_errors=True):
+                 page_size=16, max_requests=64, device="cuda:0", gemm="auto", check_device_errors=True,
+                 use_graph=False):
         """Either ``model_dir`` (config.json + model.safetensors) or ``config`` (the raw
         config.json dict) with ``tensors`` ({checkpoint name: tensor})."""
         self.device = require_cuda(device)
@@ -79,9 +80,15 @@ class Engine:
         kv_tokens = (kv_tokens + page_size - 1) // page_size * page_size
         self.cache = CacheManager(cache_needs(self.spec), kv_tokens, page_size, max_requests, self.max_context)
         self.cache.allocate(self.device, self.dtype)
-        self._caches = [self.cache.layer_view(i) for i in range(len(self.spec.layers))]
+        self._caches = [self.cache.layer_view(i) if e.cache_of is None else self.cache.layer_view(e.cache_of, writable=False)
+                        for i, e in enumerate(self.spec.run_order)]
         self.check_device_errors = check_device_errors
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.use_graph = use_graph and self.model.graph_safe
+        self._graphs, self._seen = {}, set()
+        kernels.error_flag(self.device)                 # allocated before any graph capture
+        if self.dtype == torch.bfloat16 and gemm != "simt":
+            kernels._tile_counters(self.device, 8192)
         self._meta_dev = None
         self._meta_host = []
         self._meta_events = []
@@ -137,35 +144,35 @@ class Engine:
 
     def _meta_buffers(self, n_ints):
         if self._meta_dev is None or self._meta_dev.numel() < n_ints:
-            cap = max(4096, 1 << (n_ints - 1).bit_length())
+            cap = max(1 << 16, 1 << (n_ints - 1).bit_length())
             torch.cuda.current_stream().synchronize()
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
             self._meta_events = [None, None]
+            self._graphs.clear()                 # graphs hold views of the old buffer
         self._turn ^= 1
         if self._meta_events[self._turn] is not None:
             self._meta_events[self._turn].synchronize()
         return self._meta_host[self._turn]
 
-    def _build_context(self, entries):
-        lengths = [len(e.tokens) for e in entries]
-        N, E, M = sum(lengths), len(entries), sum(len(e.want) for e in entries)
+    def _layout(self, N, E, M):
+        """Offsets of the step's int32 arrays in the metadata buffer; a function of the counts only."""
+        MB, o, at = self.cache.max_blocks, 0, {}
+        for name, n in (("ids", N), ("pos", N), ("ent", N), ("want", M), ("slot", E), ("start", E + 1), ("pos0", E)):
+            at[name] = (o, o + n)
+            o += n
+        for g in self.cache.groups:
+            at["table:" + g.name] = (o, o + E * MB)
+            o += E * MB
+        at["total"] = o
+        return at
+
+    def _fill(self, entries, lengths, at, arr):
+        N, E = sum(lengths), len(entries)
         MB = self.cache.max_blocks
-        groups = self.cache.groups
-        total = 3 * N + M + E + (E + 1) + E + len(groups) * E * MB
-        host = self._meta_buffers(total)
-        arr = host.numpy()
-        ids, pos, ent = arr[0:N], arr[N:2 * N], arr[2 * N:3 * N]
-        o = 3 * N
-        want = arr[o:o + M]; o += M
-        slot = arr[o:o + E]; o += E
-        start = arr[o:o + E + 1]; o += E + 1
-        pos0 = arr[o:o + E]; o += E
-        tables = []
-        for _ in groups:
-            tables.append(arr[o:o + E * MB].reshape(E, MB)); o += E * MB
-        cursor, wi = 0, 0
-        slots = []
+        ids, pos, ent = (arr[at[k][0]:at[k][1]] for k in ("ids", "pos", "ent"))
+        want, slot, start, pos0 = (arr[at[k][0]:at[k][1]] for k in ("want", "slot", "start", "pos0"))
+        cursor, wi, slots = 0, 0, []
         for i, e in enumerate(entries):
             n = lengths[i]
             p0 = self.cache.length[e.request]
@@ -180,37 +187,64 @@ class Engine:
             slot[i], start[i], pos0[i] = s, cursor, p0
             cursor += n
         start[E] = cursor
-        for g, table in zip(groups, tables):
-            table[:] = g.table_array[slots]
-        dev = self._meta_dev
-        dev[:total].copy_(host[:total], non_blocking=True)
+        for g in self.cache.groups:
+            a, b = at["table:" + g.name]
+            arr[a:b].reshape(E, MB)[:] = g.table_array[slots]
+        return slots, [int(x) for x in pos0]
+
+    def _context(self, N, E, M, at, decode_only, split_context, host=None):
+        dev, MB = self._meta_dev, self.cache.max_blocks
+        view = lambda k: dev[at[k][0]:at[k][1]]
+        return StepContext(
+            n_tokens=N, n_entries=E, n_wanted=M, token_ids=view("ids"), positions=view("pos"),
+            token_entry=view("ent"), want_rows=view("want"), entry_slot=view("slot"), entry_start=view("start"),
+            entry_pos0=view("pos0"),
+            block_tables={g.name: view("table:" + g.name).view(E, MB) for g in self.cache.groups},
+            host=host or {}, decode_only=decode_only, split_context=split_context, runtime=self.runtime,
+            sm_count=self.sm_count)
+
+    def _upload(self, entries, lengths, at):
+        host = self._meta_buffers(at["total"])
+        slots, pos0 = self._fill(entries, lengths, at, host.numpy())
+        self._meta_dev[:at["total"]].copy_(host[:at["total"]], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._meta_events[self._turn] = event
-        o = 3 * N
-        views = {}
-        views["want"] = dev[o:o + M]; o += M
-        views["slot"] = dev[o:o + E]; o += E
-        views["start"] = dev[o:o + E + 1]; o += E + 1
-        views["pos0"] = dev[o:o + E]; o += E
-        block_tables = {}
-        for g in groups:
-            block_tables[g.name] = dev[o:o + E * MB].view(E, MB); o += E * MB
-        decode_only = all(n == 1 for n in lengths)
-        return StepContext(
-            n_tokens=N, n_entries=E, n_wanted=M, token_ids=dev[0:N], positions=dev[N:2 * N],
-            token_entry=dev[2 * N:3 * N], want_rows=views["want"], entry_slot=views["slot"],
-            entry_start=views["start"], entry_pos0=views["pos0"], block_tables=block_tables,
-            host={"lengths": lengths, "pos0": [int(x) for x in pos0], "slots": slots},
-            decode_only=decode_only, split_context=int(max(p + n for p, n in zip(pos0, lengths))),
-            runtime=self.runtime, sm_count=self.sm_count)
+        return slots, pos0
+
+    def _run(self, entries):
+        lengths = [len(e.tokens) for e in entries]
+        N, E, M = sum(lengths), len(entries), sum(len(e.want) for e in entries)
+        at = self._layout(N, E, M)
+        decode_only = N == E
+        slots, pos0 = self._upload(entries, lengths, at)
+        host = {"lengths": lengths, "pos0": pos0, "slots": slots}
+        if self.use_graph and decode_only and M > 0:
+            key = (E, M)
+            graph = self._graphs.get(key)
+            if graph is None and key in self._seen:
+                # the second step of this shape: capture it (the first ran eagerly and warmed everything up)
+                ctx = self._context(N, E, M, at, True, self.max_context)
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.current_stream().synchronize()
+                with torch.cuda.graph(graph):
+                    static_logits = self.model.forward(ctx, self._caches)
+                self._graphs[key] = graph = (graph, static_logits)
+            if graph is not None:
+                graph[0].replay()
+                return graph[1]             # valid until the next step of this shape
+            self._seen.add(key)
+        ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host)
+        return self.model.forward(ctx, self._caches)
 
     @torch.no_grad()
     def step(self, entries, end=()):
         """Run one batch. Returns float32 logits [number of wanted places, vocab] in the order of
         the entries and of each entry's ``want`` (an empty [0, vocab] tensor if none are wanted).
         ``end``: requests that are finished after this step; what they hold is given back.
-        Raises StepError (bad batch) or PageCapacityError (no pages) with nothing changed."""
+        Raises StepError (bad batch) or PageCapacityError (no pages) with nothing changed.
+        With CUDA graphs on, the logits of a decode-only step live in a buffer that the next
+        step of the same shape overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         fresh = [e.request for e in entries if e.request not in self.cache.slot_of]
@@ -222,14 +256,13 @@ class Engine:
             for r in fresh:
                 self.cache.release(r)
             raise
-        ctx = self._build_context(entries)
-        logits = self.model.forward(ctx, self._caches)
+        logits = self._run(entries)
         for e in entries:
             self.cache.advance(e.request, self.cache.length[e.request] + len(e.tokens))
         for r in end:
             self.finish(r)
         self.steps += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         if logits is None:
             logits = torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         if self.check_device_errors:

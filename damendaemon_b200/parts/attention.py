@@ -17,6 +17,8 @@ from .spec import TensorDecl
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
         self.qkv_w = weights[spec.qkv_weight]
@@ -55,7 +57,8 @@ class Attention(Mixer):
         v = qkv[:, self.q_width + self.kv_width:]
         q, k = position.on_query_key(q, k, ctx)
         table = ctx.block_table(cache.group)
-        kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, cache.kv)
+        if cache.writable:
+            kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, cache.kv)
         attended = ctx.attention(q, cache.kv, table, s.n_heads, s.scale, s.window)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)

@@ -12,6 +12,8 @@ ACTIVATIONS = ("gelu_new", "gelu")
 
 @register_feed_forward("dense")
 class DenseFeedForward(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, weights, runtime):
         if spec.activation not in ACTIVATIONS:
             raise ValueError(f"activation {spec.activation!r} is not supported; known: {ACTIVATIONS}")

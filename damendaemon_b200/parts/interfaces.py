@@ -7,7 +7,8 @@
              on the device, block tables per cache group, scratch.
 ``cache``    a ``LayerCache`` (cache/manager.py): ``kv`` pages of this layer
              [pages, 2, kv_heads, page_size, head_dim], ``group`` (its block table is
-             ``ctx.block_table(cache.group)``), ``state`` rows [max_requests, ...].
+             ``ctx.block_table(cache.group)``), ``state`` rows [max_requests, ...],
+             ``writable`` (False when the stop reads another stop's cache).
 
 Norm              tensor_decls(spec); forward(x_f32 [N,width], row_index=None) -> [N,width] engine dtype
 PositionEncoding  tensor_decls(spec); embedding_table() -> table or None (added to the token
@@ -45,6 +46,11 @@ class Part:
 
 
 class Mixer(Part):
+    # True if forward() launches the same kernels with the same arguments whenever the step's
+    # counts are the same (everything that varies is read from device memory), so that a
+    # decode step may be replayed from a CUDA graph. Parts that plan on the host say False.
+    graph_safe = False
+
     @staticmethod
     def cache_needs(spec):
         return []
@@ -54,6 +60,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    graph_safe = False
+
     def forward(self, y, residual, ctx):
         raise NotImplementedError
 

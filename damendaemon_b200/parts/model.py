@@ -31,17 +31,24 @@ def tensor_decls(spec):
 
 
 def cache_needs(spec):
-    """One list of cache needs per layer."""
-    return [list(lookup(MIXERS, layer.mixer, "mixer").cache_needs(layer.mixer)) for layer in spec.layers]
+    """One list of cache needs per stop of the run order (empty for a stop that reads another's cache)."""
+    needs = []
+    for entry in spec.run_order:
+        mixer = spec.layers[entry.layer].mixer
+        needs.append([] if entry.cache_of is not None else list(lookup(MIXERS, mixer, "mixer").cache_needs(mixer)))
+    return needs
 
 
 class DecoderModel:
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
-        for entry in spec.run_order:
-            if not 0 <= entry.layer < len(spec.layers) or not 0 <= entry.cache_layer < len(spec.layers):
-                raise ValueError(f"run order names layer {entry.layer} (cache of {entry.cache_layer}); "
-                                 f"the model has {len(spec.layers)}")
+        for stop, entry in enumerate(spec.run_order):
+            if not 0 <= entry.layer < len(spec.layers):
+                raise ValueError(f"stop {stop} of the run order names layer {entry.layer}; the model has {len(spec.layers)}")
+            if entry.cache_of is not None and (not 0 <= entry.cache_of < stop or
+                                               spec.run_order[entry.cache_of].cache_of is not None):
+                raise ValueError(f"stop {stop} reads the cache of stop {entry.cache_of}, which must be an earlier stop "
+                                 "with a cache of its own")
         self.token_table = weights[spec.token_table]
         self.head = weights[spec.head_weight] if spec.head_weight else self.token_table
         self.position = lookup(POSITIONS, spec.position, "position encoding")(spec.position, weights, runtime)
@@ -54,16 +61,18 @@ class DecoderModel:
                 lookup(NORMS, layer.norm2, "norm")(layer.norm2, weights, runtime),
                 lookup(FEED_FORWARDS, layer.feed_forward, "feed-forward")(layer.feed_forward, weights, runtime)))
         self.final_norm = lookup(NORMS, spec.final_norm, "norm")(spec.final_norm, weights, runtime)
+        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
+                              for b in self.blocks)
 
     def forward(self, ctx, caches):
         """Run the step's tokens; float32 logits [wanted rows, vocab] (or None if none are wanted).
 
-        caches: per layer, the LayerCache view the layer's mixer reads and writes.
+        caches: per stop of the run order, the LayerCache view its mixer reads (and writes, if it is its own).
         """
         x = kernels.embed(ctx.token_ids, ctx.positions, self.token_table, self.position.embedding_table())
         x = self.position.on_embedding(x, ctx)
-        for entry in self.spec.run_order:
-            x = self.blocks[entry.layer].forward(x, ctx, caches[entry.cache_layer], self.position)
+        for stop, entry in enumerate(self.spec.run_order):
+            x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
         if ctx.n_wanted == 0:
             return None
         y = self.final_norm.forward(x, row_index=ctx.want_rows)

@@ -89,13 +89,15 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class RunEntry:
-    """One stop in the forward pass: run ``layer`` with the cache of ``cache_of``."""
+    """One stop of the forward pass: run ``layer`` (an index into ``ModelSpec.layers``).
+
+    Every stop has a cache of its own, so a layer that is named twice keeps the keys and
+    values of its two runs apart. ``cache_of`` = the index of an EARLIER STOP in
+    ``run_order`` makes this stop read that stop's cache instead: it gets no pages of its
+    own and does not write (its mixer sees ``cache.writable == False``).
+    """
     layer: int
     cache_of: Optional[int] = None
-
-    @property
-    def cache_layer(self) -> int:
-        return self.layer if self.cache_of is None else self.cache_of
 
 
 @dataclass(frozen=True)

@@ -143,16 +143,44 @@ class PlainGpt2:
         return ids[len(prompt):]
 
 
-def sample_token(logits_row, temperature, u):
+def sample_token(logits_row, temperature, u, top_k=0, top_p=1.0):
     """The engine's sampling rule, restated: greedy = first maximum; else inverse CDF.
 
-    p = softmax(logits / T) in token-id order, c = cumulative sum, the token is the first
-    index whose c exceeds u * c[-1] (the reference draws u from a per-request
-    random.Random and searches the normalised CDF, damendaemon/sampling.py:131-177).
+    Keep the top_k largest logits (ties with the k-th stay), p = softmax(logits / T) over them,
+    keep the most probable tokens until their mass reaches top_p (the crossing token and its
+    ties stay), then with c the cumulative sum in token-id order the token is the first index
+    whose c exceeds u * c[-1] (the reference draws u from a per-request random.Random and
+    searches the normalised CDF, damendaemon/sampling.py:140-177).
     """
     row = torch.as_tensor(logits_row, dtype=torch.float64)
     if not temperature:
         return int(row.argmax())
-    z = (row - row.max()) / temperature
-    c = torch.exp(z).cumsum(0)
+    keep = torch.ones_like(row, dtype=torch.bool)
+    if top_k and top_k < len(row):
+        keep &= row >= row.topk(top_k).values[-1]
+    e = torch.where(keep, torch.exp((row - row.max()) / temperature), torch.zeros_like(row))
+    if top_p < 1:
+        order = torch.argsort(row, descending=True, stable=True)
+        mass = e[order].cumsum(0)
+        crossing = int(torch.searchsorted(mass, torch.tensor(top_p * float(mass[-1]), dtype=torch.float64)))
+        keep &= row >= row[order[min(crossing, len(row) - 1)]]
+        e = torch.where(keep, e, torch.zeros_like(e))
+    c = e.cumsum(0)
     return int(min(torch.searchsorted(c, torch.tensor(u * float(c[-1]), dtype=torch.float64), right=True), len(row) - 1))
+
+
+def adjust_logits(logits_row, prompt, generated, repetition=1.0, frequency=0.0, presence=0.0, bias=None):
+    """Penalties and bias as the reference applies them (damendaemon/sampling.py:86-104): divide or
+    multiply the logits of seen tokens by the repetition penalty, subtract count * frequency +
+    presence for generated tokens, add the bias."""
+    row = torch.as_tensor(logits_row, dtype=torch.float64).clone()
+    from collections import Counter
+    counts = Counter(generated)
+    if repetition != 1:
+        for t in set(prompt) | set(counts):
+            row[t] = row[t] / repetition if row[t] > 0 else row[t] * repetition
+    for t, n in counts.items():
+        row[t] -= n * frequency + presence
+    for t, b in (bias or {}).items():
+        row[t] += b
+    return row
