@@ -1,0 +1,292 @@
+#!/usr/bin/env python3
+"""Headline benchmark: GPT-2 XL shape, random bfloat16 weights, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers N]
+
+A "step" is one decode step of the whole batch. Default run: batch 8, every request a
+512-token prompt, then W untimed and K timed decode steps (context 512 -> 1024). ``value`` is
+decoded tokens a second timed on the device with CUDA events (tokens known in advance, the
+argmax kernel included, nothing read back); ``e2e`` is the same through the Python entry
+point's scheduler: host token ids in (pinned metadata copy every step), sampled ids out
+(device-to-host read every step). Also on the line: a 2,048-token prefill (2 prompts of
+1,024), decode at batch 1 and 64, the HBM roofline of the decode step, clocks sampled
+during the timed region, and the number of kernels launched.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+XL = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 48, "n_embd": 1600, "n_head": 25,
+      "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024, "layer_norm_epsilon": 1e-5,
+      "activation_function": "gelu_new"}
+PROMPT = 512
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"])}, "measured"
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self):
+        sm, top, reasons = [], 0, set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6 or not parts[0].isdigit():
+                continue
+            sm.append(int(parts[0]))
+            top = max(top, int(parts[1]) if parts[1].isdigit() else 0)
+            reasons |= {n for n, v in zip(self.NAMES, parts[2:]) if v.lower().startswith("active")}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": top or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_runtime(config, batch, use_graph=True, seed=0):
+    import torch
+    from damendaemon_b200.registry import architecture_of
+    from damendaemon_b200.runtime import Runtime
+    arch = architecture_of(config)
+    typed = arch.parse_config(config)
+    tensors = arch.random_tensors(typed, seed, torch.bfloat16, device="cuda")
+    runtime = Runtime(None, config=config, tensors=tensors, dtype="bfloat16", max_batch=batch,
+                      kv_cache_tokens=batch * config["n_positions"], use_graph=use_graph, token_budget=4096)
+    del tensors
+    torch.cuda.empty_cache()
+    return runtime
+
+
+def random_ids(n, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def prefill_all(engine, prompts, budget=4096):
+    from damendaemon_b200.engine import StepEntry
+    names = list(prompts)
+    per = max(1, budget // max(len(p) for p in prompts.values()))
+    for i in range(0, len(names), per):
+        engine.step([StepEntry(r, prompts[r], []) for r in names[i:i + per]])
+
+
+def decode_device_timed(engine, batch, warmup, steps, vocab):
+    """K decode steps with tokens known in advance, timed on the device. Returns (ms per step, bytes per step, launches per step)."""
+    import torch
+    from damendaemon_b200 import kernels
+    from damendaemon_b200.engine import StepEntry
+    prompts = {f"d{i}": random_ids(PROMPT, vocab, 100 + i) for i in range(batch)}
+    prefill_all(engine, prompts)
+    feed = [random_ids(batch, vocab, 1000 + s) for s in range(warmup + steps)]
+
+    def one(s):
+        logits = engine.step([StepEntry(r, [feed[s][i]], [0]) for i, r in enumerate(prompts)])
+        return kernels.sample(logits)
+    # one eager step counts the kernels of a step (graph replays launch the same ones)
+    before = kernels.launches
+    one(0)
+    per_step = kernels.launches - before
+    for s in range(1, warmup):
+        one(s)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for s in range(warmup, warmup + steps):
+        one(s)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    kv_per_token = engine.cache.bytes_per_token(2)
+    contexts = [PROMPT + s + 1 for s in range(warmup, warmup + steps)]
+    position_table = engine.spec.max_positions * engine.spec.width * 2
+    bytes_per_step = engine.weight_bytes - position_table + batch * kv_per_token * statistics.mean(contexts)
+    for r in prompts:
+        engine.finish(r)
+    return ms, bytes_per_step, per_step
+
+
+def decode_end_to_end(runtime, batch, warmup, steps, vocab):
+    """The same through the scheduler: host tokens in, sampled tokens out, every step."""
+    import torch
+    from damendaemon_b200.engine.scheduler import Request, Scheduler
+    scheduler = Scheduler(runtime.engine, token_budget=4096)
+    for i in range(batch):
+        scheduler.submit(Request(random_ids(PROMPT, vocab, 100 + i), max_tokens=warmup + steps + 1, ignore_eos=True))
+    while scheduler.waiting or scheduler.prefilling:
+        scheduler.step()
+    for _ in range(warmup):
+        scheduler.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    produced = 0
+    for _ in range(steps):
+        produced += len(scheduler.step())
+    stop.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    h2d = runtime.engine.last_h2d_bytes
+    for r in scheduler.live():
+        runtime.engine.finish(r.id)
+    return produced / wall, h2d, batch * 4
+
+
+def prefill_timed(engine, vocab, repeats=5):
+    import torch
+    from damendaemon_b200.engine import StepEntry
+    times = []
+    for rep in range(2 + repeats):
+        entries = [StepEntry(f"p{rep}-{i}", random_ids(1024, vocab, 7 + i + 10 * rep), [1023]) for i in range(2)]
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step(entries, end=[e.request for e in entries])
+        stop.record()
+        torch.cuda.synchronize()
+        if rep >= 2:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def prefill_flops(c, layers, tokens_per_prompt=1024, prompts=2):
+    h, inner = c["n_embd"], c["n_inner"]
+    matrices = layers * (3 * h * h + h * h + 2 * h * inner)
+    gemm = 2 * matrices * tokens_per_prompt * prompts + 2 * prompts * c["vocab_size"] * h
+    attention = prompts * layers * 4 * (tokens_per_prompt * (tokens_per_prompt + 1) // 2) * h
+    return gemm + attention
+
+
+def reference_arm(args):
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    ref = ROOT / "baseline" / "_ref"
+    note = (ROOT / "baseline" / "UNAVAILABLE.txt")
+    why = note.read_text().strip() if note.is_file() else None
+    if why is None and not (ref / "damendaemon").is_dir():
+        why = "the reference is not installed under baseline/_ref"
+    if why is None:
+        try:
+            sys.path.insert(0, str(ROOT / "baseline"))
+            import run_reference
+            print(json.dumps(run_reference.run(args, XL, PROMPT)), flush=True)
+            return 0
+        except Exception as error:      # noqa: BLE001
+            why = f"the reference arm failed: {type(error).__name__}: {str(error)[:200]}"
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    return 0
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=480)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+    if PROMPT + args.warmup + args.steps > XL["n_positions"]:
+        args.steps = XL["n_positions"] - PROMPT - args.warmup
+    import torch
+    config = dict(XL)
+    layers = args.layers or XL["n_layer"]
+    config["n_layer"] = layers
+    vocab = config["vocab_size"]
+    peak, peak_source = peaks()
+
+    runtime = make_runtime(config, args.batch)
+    engine = runtime.engine
+    with ClockSampler() as clocks:
+        ms, step_bytes, launches_per_step = decode_device_timed(engine, args.batch, args.warmup, args.steps, vocab)
+    clock_summary = clocks.summary()
+    e2e_value, h2d, d2h = decode_end_to_end(runtime, args.batch, args.warmup, args.steps, vocab)
+    prefill_ms = prefill_timed(engine, vocab)
+    flops = prefill_flops(config, layers)
+    del runtime, engine
+    torch.cuda.empty_cache()
+
+    points = {}
+    if not args.no_points:
+        for batch in (1, 64):
+            rt = make_runtime(config, batch)
+            steps = min(args.steps, 128)
+            point_ms, _, _ = decode_device_timed(rt.engine, batch, args.warmup, steps, vocab)
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
+            del rt
+            torch.cuda.empty_cache()
+
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": f"decode tok/s at batch {args.batch} (GPT-2 XL shape, context 512->1024)",
+        "value": round(args.batch * 1000.0 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "gpt2-xl-shape", "n_layer": XL["n_layer"], "n_layer_run": layers, "n_embd": 1600, "n_head": 25,
+                   "head_dim": 64, "n_inner": 6400, "vocab_size": vocab, "n_positions": 1024, "global_batch": args.batch,
+                   "seq_len": 1024, "prompt_len": PROMPT, "page_size": 16, "kv_dtype": "bf16", "weights": "random bf16",
+                   "parallelism": "single-gpu", "l2": "inputs>L2 (3.1 GB of weights read per step)", "cuda_graph": True,
+                   "activation": "gelu_new", "peaks": peak_source},
+        "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

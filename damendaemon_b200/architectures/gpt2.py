@@ -53,20 +53,22 @@ def build_spec(c: Gpt2Config) -> ModelSpec:
     )
 
 
-def random_tensors(c: Gpt2Config, seed: int, matrix_dtype=torch.float32) -> dict:
+def random_tensors(c: Gpt2Config, seed: int, matrix_dtype=torch.float32, device="cpu") -> dict:
     """Seeded random GPT-2 weights under their checkpoint names, in a fixed draw order.
 
     Tables and matrices ~N(0, 0.02); both ``c_proj`` matrices ~N(0, 0.02/sqrt(2*n_layer));
     biases ~N(0, 0.02); LayerNorm gamma = 1 + N(0, 0.02), beta ~N(0, 0.02). Matrices and
-    tables are stored in ``matrix_dtype``; vectors stay float32.
+    tables are stored in ``matrix_dtype``; vectors stay float32. ``device``: where the numbers
+    are drawn (the CPU stream and a CUDA stream differ; a model folder is always written
+    from the CPU stream).
     """
-    g = torch.Generator(device="cpu")
+    g = torch.Generator(device=device)
     g.manual_seed(int(seed))
     h, inner = c.n_embd, c.n_inner
     out = {}
 
     def normal(shape, std, mean=0.0):
-        return torch.randn(shape, generator=g, dtype=torch.float32) * std + mean
+        return torch.randn(shape, generator=g, dtype=torch.float32, device=device) * std + mean
 
     def matrix(name, shape, std=0.02):
         out[name] = normal(shape, std).to(matrix_dtype)

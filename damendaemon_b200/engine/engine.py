@@ -207,6 +207,7 @@ class Engine:
         host = self._meta_buffers(at["total"])
         slots, pos0 = self._fill(entries, lengths, at, host.numpy())
         self._meta_dev[:at["total"]].copy_(host[:at["total"]], non_blocking=True)
+        self.last_h2d_bytes = at["total"] * 4
         event = torch.cuda.Event()
         event.record()
         self._meta_events[self._turn] = event

@@ -67,7 +67,12 @@ def library(name):
         return lib
 
 
-def _call(lib, fn, *args):
+launches = 0          # kernels launched through this module (what the bench reports as gpu_launches)
+
+
+def _call(lib, fn, *args, n_kernels=1):
+    global launches
+    launches += n_kernels
     code = getattr(lib, fn)(*args)
     if code:
         raise KernelError(lib.dd_last_error().decode())
@@ -201,7 +206,7 @@ def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), n, n_heads, kv_heads, head_dim, page_size, n_pages,
           0 if window is None else int(window), float(scale), int(n_splits), _dt(q.dtype),
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), n_kernels=2 if n_splits > 1 else 1)
     return out
 
 
