@@ -222,3 +222,63 @@ DD_API int dd_attention_rows(const void* q, int q_stride, const void* cache, con
                                           page_size, n_pages, window, scale, n_splits, error_flag, s);
     return dd_fail("dd_attention_rows: unknown dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The variant for callers that cannot allocate (declared and described in no_alloc.h). The split
+// scratch lives in this library's image; host code may not use the array's name as an address,
+// so the device address is looked up once per device and handed to the same kernels as above.
+#include "no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) unsigned char dd_static_scratch[DD_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch[MAX_DEVICES] = {};
+std::mutex g_static_mutex;
+
+// The device address of dd_static_scratch on the current device, looked up on first use.
+int static_scratch(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return dd_fail("dd_attention_rows_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return dd_fail("dd_attention_rows_static: device %d is beyond %d", dev, MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_scratch[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, dd_static_scratch);
+        if (e != cudaSuccess || !p)
+            return dd_fail("dd_attention_rows_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_scratch[dev] = static_cast<float*>(p);
+    }
+    *ptr = g_static_scratch[dev];
+    return 0;
+}
+}  // namespace
+
+DD_API int dd_attention_rows_static(const void* q, int q_stride, const void* cache, const int* tok_entry,
+                                    const int* tok_pos, const int* block_table, int max_blocks, void* out,
+                                    int out_stride, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                    int page_size, int n_pages, int window, float scale, int n_splits, int dtype,
+                                    int* error_flag, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_splits < 1) return dd_fail("dd_attention_rows_static: n_splits=%d", n_splits);
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (n_splits > 1) {
+        if (n_heads <= 0 || head_dim <= 0) return dd_fail("dd_attention_rows_static: bad sizes");
+        const unsigned long long items = (unsigned long long)n_tokens * n_heads * n_splits;
+        const unsigned long long need = items * (unsigned long long)(head_dim + 2) * sizeof(float);
+        if (need > DD_STATIC_SCRATCH_BYTES)
+            return dd_fail("dd_attention_rows_static: %d tokens x %d heads x %d splits x head size %d need %llu bytes of "
+                           "scratch; the built-in scratch holds %u (use dd_attention_rows with your own buffers, or fewer splits)",
+                           n_tokens, n_heads, n_splits, head_dim, need, DD_STATIC_SCRATCH_BYTES);
+        float* base = nullptr;
+        if (int e = static_scratch(&base)) return e;
+        part_o = base;                                   // [items, head_dim]
+        part_ml = base + items * head_dim;               // [items, 2]
+    }
+    return dd_attention_rows(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride, part_o,
+                             part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages, window, scale,
+                             n_splits, dtype, error_flag, stream);
+}

@@ -33,7 +33,7 @@ LIBRARIES = {
              "sampling.cu"],
     "tensor": ["errors.cu", "gemm_tcgen05.cu", "attention_decode.cu", "attention_prefill.cu"],
 }
-HEADERS = ["common.cuh", "tcgen05.cuh"]
+HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
