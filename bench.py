@@ -226,6 +226,7 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    parser.add_argument("--no-graph", action="store_true", help="launch every decode kernel eagerly (for profilers)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -243,7 +244,7 @@ def main():
     vocab = config["vocab_size"]
     peak, peak_source = peaks()
 
-    runtime = make_runtime(config, args.batch)
+    runtime = make_runtime(config, args.batch, use_graph=not args.no_graph)
     engine = runtime.engine
     with ClockSampler() as clocks:
         ms, step_bytes, launches_per_step = decode_device_timed(engine, args.batch, args.warmup, args.steps, vocab)
@@ -257,7 +258,7 @@ def main():
     points = {}
     if not args.no_points:
         for batch in (1, 64):
-            rt = make_runtime(config, batch)
+            rt = make_runtime(config, batch, use_graph=not args.no_graph)
             steps = min(args.steps, 128)
             point_ms, _, _ = decode_device_timed(rt.engine, batch, args.warmup, steps, vocab)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
@@ -273,7 +274,7 @@ def main():
         "config": {"model": "gpt2-xl-shape", "n_layer": XL["n_layer"], "n_layer_run": layers, "n_embd": 1600, "n_head": 25,
                    "head_dim": 64, "n_inner": 6400, "vocab_size": vocab, "n_positions": 1024, "global_batch": args.batch,
                    "seq_len": 1024, "prompt_len": PROMPT, "page_size": 16, "kv_dtype": "bf16", "weights": "random bf16",
-                   "parallelism": "single-gpu", "l2": "inputs>L2 (3.1 GB of weights read per step)", "cuda_graph": True,
+                   "parallelism": "single-gpu", "l2": "inputs>L2 (3.1 GB of weights read per step)", "cuda_graph": not args.no_graph,
                    "activation": "gelu_new", "peaks": peak_source},
         "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},

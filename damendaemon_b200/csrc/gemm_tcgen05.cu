@@ -51,12 +51,23 @@ template <int BN> struct Config {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void store_out(const GemmParams& p, int m, int n, float v) {
-    if (p.bias) v += p.bias[n];
-    v = dd_activation(v, p.act);
-    if (p.residual) v += p.residual[(size_t)m * p.ldr + n];
-    if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-    else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+// Epilogue of 16 consecutive tokens (m_first ..) of one output feature n. The residual may be
+// the output itself, so all 16 residual values are read before anything is written: the loads
+// stay independent instead of being ordered behind each store.
+__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc) {
+    const float b = p.bias ? p.bias[n] : 0.f;
+    float r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        r[j] = (p.residual && m_first + j < p.M) ? p.residual[(size_t)(m_first + j) * p.ldr + n] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int m = m_first + j;
+        if (m >= p.M) break;
+        const float v = dd_activation(acc[j] + b, p.act) + r[j];
+        if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+    }
 }
 
 template <int BN>
@@ -159,11 +170,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         for (int j = 0; j < 16; ++j) r[j] = 0;
                     }
                     if (n_ok) {
+                        float acc[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int m = m0 + c0 + j;
-                            if (m < p.M) store_out(p, m, n, __uint_as_float(r[j]));
-                        }
+                        for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(r[j]);
+                        store_out16(p, m0 + c0, n, acc);
                     }
                 }
             }
@@ -196,11 +206,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (*last_flag) {
                 __threadfence();
                 if (n_ok && !*abort_flag) {
-                    for (int m = m0; m < min(p.M, m0 + BN); ++m) {
-                        float v = 0.f;
-                        for (int s = 0; s < p.splits; ++s)
-                            v += __ldcg(p.workspace + ((size_t)s * p.M + m) * p.N + n);
-                        store_out(p, m, n, v);
+                    // 16 tokens at a time, so that 16 independent loads are in flight for every split
+                    for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        // splits are added in ascending order (deterministic), four splits' loads in flight at once
+                        for (int s0 = 0; s0 < p.splits; s0 += 2) {
+                            float t[2][16];
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                const float* src = p.workspace + ((size_t)(s0 + u) * p.M + m0 + c0) * p.N + n;
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    t[u][j] = (s0 + u < p.splits && m0 + c0 + j < p.M) ? __ldcg(src + (size_t)j * p.N) : 0.f;
+                            }
+#pragma unroll
+                            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) v[j] += t[u][j];
+                        }
+                        store_out16(p, m0 + c0, n, v);
                     }
                 }
                 if (warp == 2 && lane == 0) p.counters[tile] = 0;
@@ -272,11 +298,12 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     if (token_tile) *token_tile = bn;
     const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
     const int kblocks = dd_ceil_div(K, BK);
+    // Splitting K costs a round trip through the workspace (a few microseconds of latency), so it pays only
+    // when few CTAs would each stream a long K: a handful of tokens, few tiles, at least 64 k-blocks.
     int splits = 1;
-    if (tiles * 3 < sm_count * 2) {
-        splits = dd_ceil_div(sm_count, tiles);
-        if (splits > kblocks / 2) splits = kblocks / 2;
-        if (splits > 16) splits = 16;
+    if (M <= 16 && kblocks >= 64 && tiles * 4 < sm_count) {
+        splits = dd_ceil_div(sm_count, 2 * tiles);
+        if (splits > 8) splits = 8;
         if (splits < 1) splits = 1;
     }
     return splits;

@@ -30,14 +30,19 @@ class StepContext:
     def block_table(self, group):
         return self.block_tables[group.name]
 
-    def key_splits(self, n_heads):
+    def key_splits(self, n_heads, keys_per_block=64, blocks_per_sm=16):
         """How many pieces each row's keys are cut into so that a decode-only step fills the GPU."""
         if not self.decode_only:
             return 1
-        want = (self.sm_count * 16) // max(1, self.n_tokens * n_heads)
-        return max(1, min(want, (self.split_context + 63) // 64, 32))
+        want = -(-(self.sm_count * blocks_per_sm) // max(1, self.n_tokens * n_heads))
+        return max(1, min(want, (self.split_context + keys_per_block - 1) // keys_per_block, 32))
 
     def attention(self, q, kv, table, n_heads, scale, window=None):
         """Paged causal attention of this step's tokens over the cache."""
+        kv_heads, head_dim = kv.shape[2], kv.shape[4]
+        if self.decode_only and self.runtime.attention != "rows" and \
+                kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
+            return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
+                                            n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=4))
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                       n_splits=self.key_splits(n_heads))

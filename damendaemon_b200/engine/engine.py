@@ -88,7 +88,8 @@ class Engine:
         self._graphs, self._seen = {}, set()
         kernels.error_flag(self.device)                 # allocated before any graph capture
         if self.dtype == torch.bfloat16 and gemm != "simt":
-            kernels._tile_counters(self.device, 8192)
+            heads = max((getattr(l.mixer, "n_heads", 1) for l in self.spec.layers), default=1)
+            kernels._tile_counters(self.device, max(8192, max_requests * heads))
         self._meta_dev = None
         self._meta_host = []
         self._meta_events = []

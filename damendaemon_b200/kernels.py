@@ -37,6 +37,9 @@ _SIGNATURES = {
     },
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_attention_decode_supported": [_c_int] * 4,
+        "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void,
+                                _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 7
                            + [_c_void, _c_void, _c_int, _c_void, _c_void],
     },
@@ -246,6 +249,8 @@ _sm_count = {}
 def _tile_counters(device, n):
     key = torch.device(device).index or 0
     if key not in _counters or _counters[key].numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"{n} split counters are needed during a graph capture; size them before (kernels._tile_counters)")
         _counters[key] = torch.zeros(max(n, 8192), dtype=torch.int32, device=device)
     return _counters[key]
 
@@ -285,4 +290,30 @@ def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None
           0 if residual is None else residual.stride(0), _ptr(out, "out", out_dtype), out.stride(0), M, N, K,
           ACTIVATIONS[activation], _dt(out_dtype), splits, token_tile, _ptr(workspace), _ptr(counters), n_counters,
           _ptr(error_flag(a.device)), _stream())
+    return out
+
+
+def attention_decode_supported(n_heads, kv_heads, head_dim, dtype):
+    return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_decode_supported(n_heads, kv_heads, head_dim, BF16))
+
+
+def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None):
+    """Decode attention (one query per token) over a bfloat16 cache; see attention_decode_supported."""
+    n_pages, _, kv_heads, page_size, head_dim = cache.shape
+    n = q.shape[0]
+    if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
+            or not cache.is_contiguous():
+        raise KernelError("attention_decode: q does not fit the cache")
+    if out is None:
+        out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    part_o = part_ml = counters = None
+    if n_splits > 1:
+        part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+        counters = _tile_counters(q.device, n * n_heads)
+    _call(library("tensor"), "dd_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
+          _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
+          _ptr(part_o), _ptr(part_ml), _ptr(counters), n, n_heads, kv_heads, head_dim, page_size, n_pages,
+          0 if window is None else int(window), float(scale), int(n_splits), _ptr(error_flag(q.device)), _stream())
     return out

@@ -159,6 +159,25 @@ def test_attention_rows_split_decode(K, dtype, n_splits):
     assert (out.float() - one.float()).abs().max() < tol(dtype)
 
 
+@pytest.mark.parametrize("d,heads,page", [(64, 5, 16), (128, 3, 8), (64, 25, 16)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_bf16(K, d, heads, page, n_splits, window):
+    """The bfloat16 decode kernel: contexts from 1 to 1000 keys, a far key that stands out, fragmented pages."""
+    K.library("tensor")
+    assert K.attention_decode_supported(heads, heads, d, torch.bfloat16)
+    assert not K.attention_decode_supported(heads, 1, d, torch.bfloat16) or heads == 1
+    assert not K.attention_decode_supported(heads, heads, 48, torch.bfloat16)
+    c = paged_case(K, torch.bfloat16, heads, heads, d, page, lengths=[300, 33, 1, 1000, 129], new=[1, 1, 1, 1, 1],
+                   window=window, n_splits=n_splits, spike=5 if window is None else 250)
+    out = K.attention_decode(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window, n_splits=n_splits)
+    again = K.attention_decode(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window, n_splits=n_splits)
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    assert torch.equal(out, again), "the split counters were not left at zero"
+
+
 def test_attention_rejects_bad_sizes(K):
     cache = torch.zeros(4, 2, 2, 16, 20, device=DEV)
     q = torch.zeros(1, 40, device=DEV)
