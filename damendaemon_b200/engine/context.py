@@ -44,5 +44,8 @@ class StepContext:
                 kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
             return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                             n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=4))
+        if not self.decode_only and self.runtime.attention != "rows" and \
+                kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
+            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                       n_splits=self.key_splits(n_heads))

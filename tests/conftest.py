@@ -27,6 +27,13 @@ TINY_B = {
     "layer_norm_epsilon": 1e-6, "activation_function": "gelu",
     "scale_attn_by_inverse_layer_idx": True,
 }
+# a third one with head size 64, the size the tensor-core attention kernels take
+TINY_C = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 192, "n_head": 3, "n_inner": 400, "vocab_size": 331, "n_positions": 320,
+    "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_by_inverse_layer_idx": False,
+}
 
 
 @pytest.fixture(scope="session")

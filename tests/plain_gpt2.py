@@ -109,10 +109,18 @@ def mlp_block(x, w, prefix, activation):
     return conv1d(g, w[prefix + "mlp.c_proj.weight"], w[prefix + "mlp.c_proj.bias"])
 
 
-def logits_of(config, w, ids):
-    """Logits at every position of one whole sequence, [T, vocab]  (damendaemon/gpt2.py:42-66)."""
+def logits_of(config, w, ids, rounded=None):
+    """Logits at every position of one whole sequence, [T, vocab]  (damendaemon/gpt2.py:42-66).
+
+    ``rounded``: a dtype (torch.bfloat16) to which the activations that a reduced-precision engine
+    stores between kernels are rounded (norm outputs, q/k/v, attended values, the activated MLP
+    hidden); the residual stream and all arithmetic stay wide. It shows how far rounding alone
+    moves the logits of a given model, which is what a bfloat16 tolerance has to allow for.
+    """
+    keep = (lambda t: t) if rounded is None else (lambda t: t.to(rounded).to(t.dtype))
     ids = torch.as_tensor(ids, dtype=torch.long)
     h, H = config["n_embd"], config["n_head"]
+    T = len(ids)
     eps = config.get("layer_norm_epsilon", 1e-5)
     activation = config.get("activation_function", "gelu_new")
     x = embed(ids, w["wte.weight"], w["wpe.weight"])
@@ -121,9 +129,16 @@ def logits_of(config, w, ids):
         scale = (h // H) ** -0.5
         if config.get("scale_attn_by_inverse_layer_idx", False):
             scale = scale / (i + 1)
-        x = x + attention_block(layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps), w, p, H, scale)
-        x = x + mlp_block(layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps), w, p, activation)
-    x = layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps)
+        y = keep(layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps))
+        qkv = keep(conv1d(y, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"]))
+        q, k, v = (part.reshape(T, H, h // H) for part in qkv.split(h, dim=-1))
+        o = keep(causal_attention(q, k, v, scale).reshape(T, h))
+        x = x + conv1d(o, w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"])
+        y = keep(layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps))
+        u = conv1d(y, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"])
+        g = keep(gelu_new(u) if activation == "gelu_new" else gelu_erf(u))
+        x = x + conv1d(g, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
+    x = keep(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps))
     return x @ w["wte.weight"].t()          # tied head, no bias (damendaemon/gpt2.py:18,66)
 
 
@@ -131,8 +146,8 @@ class PlainGpt2:
     def __init__(self, folder, dtype=torch.float64):
         self.config, self.w = read_folder(folder, dtype)
 
-    def logits(self, ids):
-        return logits_of(self.config, self.w, ids)
+    def logits(self, ids, rounded=None):
+        return logits_of(self.config, self.w, ids, rounded)
 
     def greedy(self, prompt, n_new):
         ids = list(prompt)

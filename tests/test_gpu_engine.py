@@ -4,30 +4,40 @@ so few pages that they are used again."""
 import pytest
 import torch
 
-from conftest import TINY_A, TINY_B
+from conftest import TINY_A, TINY_B, TINY_C
 from model_tools import make_model, random_requests
 from plain_gpt2 import PlainGpt2
 from trace_tools import mixed_steps, portion_steps, run_trace, tail_steps, whole_steps
 
 pytestmark = pytest.mark.gpu
 
-CASES = {"A": (TINY_A, 0, [5, 17, 33, 100, 128, 64]), "B": (TINY_B, 1, [1, 9, 64, 200, 256, 77])}
-# float32: the engine's contract (1e-4). bfloat16: activations are rounded to 8 bits of mantissa
-# (relative 2^-9) a dozen times per layer on logits of size ~1.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+# name: (config, seed, request lengths, factor on the QKV projection that makes attention peaky)
+CASES = {"A": (TINY_A, 0, [5, 17, 33, 100, 128, 64], 8.0), "B": (TINY_B, 1, [1, 9, 64, 200, 256, 77], 8.0),
+         "C": (TINY_C, 2, [1, 70, 320, 129, 64, 200], 3.0)}
+# float32: the engine's contract. bfloat16: three times what rounding the stored activations to
+# bfloat16 does to the plain implementation's own logits for that model (measured in the fixture,
+# about 0.005 for these models), plus a small floor.
+FLOAT32_TOL = 1e-4
+TOL = {}
 
 
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for name, (config, seed, lengths) in CASES.items():
+    for name, (config, seed, lengths, sharpen) in CASES.items():
         for dtype in ("float32", "bfloat16"):
-            folder = make_model(root / f"{name}-{dtype}", config, seed, dtype)
+            folder = make_model(root / f"{name}-{dtype}", config, seed, dtype, sharpen)
             requests = random_requests(config, lengths, 100 + seed)
             plain = PlainGpt2(folder)
             want = {r: plain.logits(t).float() for r, t in requests.items()}
             out[name, dtype] = (folder, config, requests, want)
+            if dtype == "bfloat16":
+                moved = max((plain.logits(t, rounded=torch.bfloat16).float() - want[r]).abs().max().item()
+                            for r, t in requests.items())
+                TOL[name, dtype] = 3.0 * moved + 2e-3
+            else:
+                TOL[name, dtype] = FLOAT32_TOL
     return out
 
 
@@ -69,11 +79,11 @@ def compare(got, want, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cuttings(models, name, dtype, mode):
     folder, config, requests, want = models[name, dtype]
-    page = 16 if name == "A" else 8
+    page = {"A": 16, "B": 8, "C": 16}[name]
     if mode == "mixed":
         builder, peak = mixed_steps(requests, seed=3)
         kv = peak
@@ -82,7 +92,7 @@ def test_cuttings(models, name, dtype, mode):
         kv = 64 * ((config["n_positions"] + 63) // 64)
     engine = engine_for(folder, dtype, kv, page)
     got = replay(engine, builder)
-    compare(got, want, TOL[dtype], f"{name} {dtype} {mode}")
+    compare(got, want, TOL[name, dtype], f"{name} {dtype} {mode}")
     assert engine.cache.used_tokens == 0 and not engine.live_requests()
     if mode == "mixed":
         handed_out = sum((len(t) + page - 1) // page for t in requests.values())
@@ -109,7 +119,7 @@ def test_long_decoding_and_first_tokens(models, dtype):
     for p, t in enumerate(tokens):
         row = engine.step([StepEntry("x", [t], [0])]).cpu()[0]
         err = (row - want["r4"][p]).abs().max().item()
-        assert err < TOL[dtype], f"position {p}: {err:.3e}"
+        assert err < TOL["B", dtype], f"position {p}: {err:.3e}"
     # the learned positions end here: one more token must be refused and change nothing
     before = engine.length("x")
     with pytest.raises(StepError, match="positions"):
@@ -145,4 +155,4 @@ def test_trace_run_program(models, dtype, tmp_path):
     builder, peak = mixed_steps(requests, seed=11)
     outputs = run_trace(folder, dtype, builder.steps, tmp_path / "out", max_tokens=peak, page_size=16)
     got = {r: {p: torch.from_numpy(row.copy()) for p, row in rows.items()} for r, rows in builder.collect(outputs).items()}
-    compare(got, want, TOL[dtype], f"trace_run {dtype}")
+    compare(got, want, TOL["A", dtype], f"trace_run {dtype}")

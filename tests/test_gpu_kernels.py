@@ -178,6 +178,29 @@ def test_attention_decode_bf16(K, d, heads, page, n_splits, window):
     assert torch.equal(out, again), "the split counters were not left at zero"
 
 
+@pytest.mark.parametrize("d,heads,kv_heads,page", [(64, 5, 5, 16), (128, 4, 2, 8), (64, 6, 1, 32)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prefill_bf16(K, d, heads, kv_heads, page, window):
+    """The tensor-core kernel: whole prompts, a portion that continues 300 cached keys, single tokens, a far key."""
+    K.library("tensor")
+    assert K.attention_prefill_supported(heads, kv_heads, d, torch.bfloat16)
+    assert not K.attention_prefill_supported(heads, kv_heads, 48, torch.bfloat16)
+    lengths, new = [150, 1, 365, 64, 700, 65], [150, 1, 65, 64, 1, 3]
+    c = paged_case(K, torch.bfloat16, heads, kv_heads, d, page, lengths=lengths, new=new, window=window, n_splits=1,
+                   spike=3 if window is None else None)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    entry_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    entry_pos0 = torch.tensor([L - n for L, n in zip(lengths, new)], dtype=torch.int32, device=DEV)
+    out = K.attention_prefill(c["q"], c["cache"], entry_start, entry_pos0, c["table"], heads, c["scale"], window)
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    rows = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window)
+    assert (out.float() - rows.float()).abs().max() < tol(torch.bfloat16)
+
+
 def test_attention_rejects_bad_sizes(K):
     cache = torch.zeros(4, 2, 2, 16, 20, device=DEV)
     q = torch.zeros(1, 40, device=DEV)
