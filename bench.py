@@ -227,12 +227,18 @@ def main():
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     parser.add_argument("--no-graph", action="store_true", help="launch every decode kernel eagerly (for profilers)")
+    parser.add_argument("--kernel-case", help="time one kernel alone at XL shape (see damendaemon_b200/kernel_cases.py)")
+    parser.add_argument("--case-iters", type=int, default=50)
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.kernel_case:
+        from damendaemon_b200.kernel_cases import time_case
+        print(json.dumps(time_case(args.kernel_case, args.case_iters)), flush=True)
+        return 0
     if args.warmup < 3:
         args.warmup = 3
     if PROMPT + args.warmup + args.steps > XL["n_positions"]:

@@ -1,0 +1,96 @@
+"""Single kernels at GPT-2 XL shapes, for timing and for profiler captures.
+
+``python bench.py --kernel-case NAME [--case-iters N]`` builds the inputs of one case, runs the
+kernel N times back to back (rotating through enough copies of the big operand that the 126 MB
+L2 cannot hold them) and prints the time per launch from CUDA events. A profiler is pointed at
+the same command with a small N.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+
+H, D, PAGE = 25, 64, 16
+SHAPES = {"qkv": (4800, 1600, "bias"), "proj": (1600, 1600, "residual"), "fc": (6400, 1600, "gelu"),
+          "fc2": (1600, 6400, "residual"), "head": (50257, 1600, "none")}
+
+
+def _gemm_case(name, tokens, dev):
+    features, reduction, epilogue = SHAPES[name]
+    copies = max(2, min(24, (300 << 20) // (features * reduction * 2)))
+    weights = [torch.randn(features, reduction, device=dev).mul_(0.02).to(torch.bfloat16) for _ in range(copies)]
+    bias = torch.randn(features, device=dev)
+    x = torch.randn(tokens, reduction, device=dev).to(torch.bfloat16)
+    stream = torch.zeros(tokens, features, device=dev)
+    out16 = torch.empty(tokens, features, device=dev, dtype=torch.bfloat16)
+
+    def run(i):
+        w = weights[i % copies]
+        if epilogue == "bias":
+            K.gemm_tcgen05(x, w, bias, out=out16)
+        elif epilogue == "gelu":
+            K.gemm_tcgen05(x, w, bias, activation="gelu_new", out=out16)
+        elif epilogue == "residual":
+            K.gemm_tcgen05(x, w, bias, residual=stream, out_dtype=torch.float32, out=stream)
+        else:
+            K.gemm_tcgen05(x, w, out_dtype=torch.float32, out=stream)
+    work = {"bytes": features * reduction * 2, "flops": 2 * tokens * features * reduction}
+    return run, work
+
+
+def _cache_case(batch, context, dev, copies):
+    n_pages = batch * ((context + PAGE - 1) // PAGE)
+    caches = [torch.randn(n_pages, 2, H, PAGE, D, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, -1)
+    return caches, table
+
+
+def _decode_case(batch, context, dev):
+    copies = max(2, min(12, (300 << 20) // (batch * context * H * D * 4)))
+    caches, table = _cache_case(batch, context, dev, copies)
+    ent = torch.arange(batch, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+    q = torch.randn(batch, H * D, device=dev).to(torch.bfloat16)
+    want = -(-(K.sm_count(dev) * 4) // (batch * H))
+    splits = max(1, min(want, (context + 127) // 128, 32))
+    run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, None, n_splits=splits)
+    return run, {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
+
+
+def _prefill_case(prompts, length, dev):
+    caches, table = _cache_case(prompts, length, dev, 4)
+    start = torch.arange(prompts + 1, dtype=torch.int32, device=dev) * length
+    pos0 = torch.zeros(prompts, dtype=torch.int32, device=dev)
+    q = torch.randn(prompts * length, H * D, device=dev).to(torch.bfloat16)
+    run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None)
+    return run, {"bytes": prompts * length * H * D * 6, "flops": prompts * 4 * (length * (length + 1) // 2) * H * D}
+
+
+def build(name, device="cuda:0"):
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> | attn_prefill"""
+    K.library("core"), K.library("tensor")
+    parts = name.split("_")
+    if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
+        return _gemm_case(parts[1], int(parts[2][1:]), device)
+    if name.startswith("attn_decode_b"):
+        return _decode_case(int(name[len("attn_decode_b"):]), 768, device)
+    if name == "attn_prefill":
+        return _prefill_case(2, 1024, device)
+    raise ValueError(f"unknown kernel case {name!r}")
+
+
+def time_case(name, iters=50, device="cuda:0"):
+    run, work = build(name, device)
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(iters):
+        run(i)
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1000.0 / iters
+    return {"case": name, "us_per_launch": round(us, 2), "GB_per_s": round(work["bytes"] / us / 1e3, 1),
+            "TFLOP_per_s": round(work["flops"] / us / 1e6, 1), "iters": iters}
