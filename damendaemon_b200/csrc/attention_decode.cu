@@ -38,6 +38,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     __shared__ float sh_o[WARPS][D];
     __shared__ float sh_ml[WARPS][2];
     __shared__ int sh_last;
+    dd_launch_dependents();
+    dd_grid_wait();
 
     const int split = blockIdx.x, n_splits = gridDim.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -207,11 +209,11 @@ DD_API int dd_attention_decode(const void* q, int q_stride, const void* cache, c
     const float scale_log2e = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
-        attention_decode_kernel<64><<<grid, WARPS * 32, 0, s>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
+        dd_launch(attention_decode_kernel<64>, dim3(grid), dim3(WARPS * 32), 0, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
             n_heads, page_size, n_pages, window, scale_log2e, error_flag);
     else
-        attention_decode_kernel<128><<<grid, WARPS * 32, 0, s>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
+        dd_launch(attention_decode_kernel<128>, dim3(grid), dim3(WARPS * 32), 0, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
             n_heads, page_size, n_pages, window, scale_log2e, error_flag);
     return dd_check_launch("dd_attention_decode");

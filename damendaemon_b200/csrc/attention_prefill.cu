@@ -54,6 +54,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + BQ * D * 2;            // [2][BKV][D]
     uint8_t* sV = sK + 2 * BKV * D * 2;       // [2][BKV][D]
+    dd_launch_dependents();
+    dd_grid_wait();
 
     // which 64-row tile of which entry is this block's?
     int e = 0, tile = blockIdx.x, len = 0;
@@ -244,7 +246,7 @@ int launch(const void* q, int q_stride, const void* cache, const int* entry_star
     }
     // an upper bound of the number of 64-row tiles; blocks beyond the real count return at once
     dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, H);
-    attention_prefill_kernel<D><<<grid, THREADS, SMEM, s>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
+    dd_launch(attention_prefill_kernel<D>, dim3(grid), dim3(THREADS), SMEM, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
         entry_start, entry_pos0, n_entries, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, H, KH, P, n_pages,
         window, scale * 1.4426950408889634f, error_flag);
     return dd_check_launch("dd_attention_prefill");

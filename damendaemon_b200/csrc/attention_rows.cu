@@ -49,6 +49,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale,
                       int n_splits, int* __restrict__ error_flag) {
     extern __shared__ float q_smem[];
+    dd_launch_dependents();
+    dd_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
     if (item >= (long long)n_tokens * H * n_splits) return;
@@ -147,6 +149,8 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        T* __restrict__ out, int out_stride, int n_tokens, int H, int d, int n_splits) {
+    dd_launch_dependents();
+    dd_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * WARPS + warp;   // (token, head)
     if (row >= (long long)n_tokens * H) return;
@@ -176,7 +180,7 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
     const int grid = dd_ceil_div(items, WARPS);
     const size_t smem = (size_t)WARPS * d * sizeof(float);
 #define DD_ROWS(DPL)                                                                                        \
-    attention_rows_kernel<T, DPL><<<grid, WARPS * 32, smem, s>>>((const T*)q, q_stride, (const T*)cache,    \
+    dd_launch(attention_rows_kernel<T, DPL>, dim3(grid), dim3(WARPS * 32), smem, s, (const T*)q, q_stride, (const T*)cache,    \
         tok_entry, tok_pos, block_table, max_blocks, (T*)out, out_stride, part_o, part_ml, n_tokens, H, KH, \
         d, P, n_pages, window, scale, n_splits, error_flag)
     if (d <= 32) DD_ROWS(1);
@@ -186,7 +190,7 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
 #undef DD_ROWS
     if (int e = dd_check_launch("dd_attention_rows")) return e;
     if (n_splits > 1) {
-        attention_merge_kernel<T><<<dd_ceil_div((long long)n_tokens * H, WARPS), WARPS * 32, 0, s>>>(
+        dd_launch(attention_merge_kernel<T>, dim3(dd_ceil_div((long long)n_tokens * H, WARPS)), dim3(WARPS * 32), 0, s, 
             part_o, part_ml, (T*)out, out_stride, n_tokens, H, d, n_splits);
         return dd_check_launch("dd_attention_merge");
     }

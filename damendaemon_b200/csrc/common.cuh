@@ -48,3 +48,30 @@ __device__ __forceinline__ float dd_activation(float u, int act) {
 }
 
 static inline int dd_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Programmatic dependent launch. Every kernel of this library is launched so that it may start
+// while the kernel before it on the stream is still running: it does whatever does not depend
+// on earlier kernels (barrier set-up, TMEM allocation, prefetching weights), lets its own
+// successor start early (dd_launch_dependents) and then waits for the kernel before it to have
+// finished and flushed its writes (dd_grid_wait) before it reads or writes anything else in
+// global memory. Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void dd_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dd_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int dd_pdl_enabled;      // errors.cu; switched by dd_set_pdl()
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dd_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}

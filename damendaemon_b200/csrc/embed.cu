@@ -8,6 +8,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
                              const T* __restrict__ wte, const T* __restrict__ wpe,
                              float* __restrict__ out, int width, int vocab, int n_positions,
                              int* __restrict__ error_flag) {
+    dd_launch_dependents();
+    dd_grid_wait();
     const int row = blockIdx.x;
     int id = ids[row];
     int p = wpe ? pos[row] : 0;
@@ -35,10 +37,10 @@ DD_API int dd_embed(const int* ids, const int* pos, const void* wte, const void*
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == DD_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)wte, (const float*)wpe, out,
+        dd_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, pos, (const float*)wte, (const float*)wpe, out,
                                                          width, vocab, n_positions, error_flag);
     else if (table_dtype == DD_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(ids, pos, (const __nv_bfloat16*)wte,
+        dd_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids, pos, (const __nv_bfloat16*)wte,
                                                                  (const __nv_bfloat16*)wpe, out, width, vocab,
                                                                  n_positions, error_flag);
     else

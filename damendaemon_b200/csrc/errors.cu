@@ -19,6 +19,16 @@ int dd_check_launch(const char* what) {
     return 0;
 }
 
+int dd_pdl_enabled = 1;
+
+// 1 (default): kernels are launched with programmatic stream serialization, so each may start
+// its set-up while its predecessor still runs; 0: ordinary stream order. Returns the old value.
+DD_API int dd_set_pdl(int enabled) {
+    const int old = dd_pdl_enabled;
+    dd_pdl_enabled = enabled ? 1 : 0;
+    return old;
+}
+
 DD_API const char* dd_last_error() { return g_message; }
 
 // Compute capability of the current device as major*10+minor, or a negative CUDA error.

@@ -16,6 +16,8 @@ gemm_simt_kernel(const TI* __restrict__ A, int lda, const TI* __restrict__ W, in
                  TO* C, int ldc, int M, int N, int K, int act) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    dd_launch_dependents();
+    dd_grid_wait();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;
@@ -70,7 +72,7 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, co
            void* C, int ldc, int M, int N, int K, int act, cudaStream_t s) {
     dim3 grid(dd_ceil_div(N, BN), dd_ceil_div(M, BM));
     if (grid.y > 65535) return dd_fail("dd_gemm_simt: too many rows (%d)", M);
-    gemm_simt_kernel<TI, TO><<<grid, THREADS, 0, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
+    dd_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(THREADS), 0, s, (const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
                                                      (TO*)C, ldc, M, N, K, act);
     return dd_check_launch("dd_gemm_simt");
 }

@@ -121,6 +121,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    dd_launch_dependents();      // the next kernel may begin its own set-up now
 
     // Work item -> (feature tile, token tile, split). Feature tiles vary fastest, so CTAs that run
     // side by side share the same token tile in L2.
@@ -138,14 +139,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc::prefetch_tensormap(&map_x);
             uint32_t it = 0;                               // k-blocks issued so far, across items
             bool ok = true;
+            // Weights never change, so the weight tiles of the first stages are requested before the
+            // kernel that produces the activations has finished; the activation tiles follow the wait.
+            int ahead = 0;
+            if (blockIdx.x < n_items) {
+                DD_ITEM_COORDS(blockIdx.x)
+                (void)m0;
+                ahead = min(n_kblocks, C::STAGES);
+                for (int i = 0; i < ahead; ++i) {
+                    tc::mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+                    tc::tma_load_2d(tiles + i * C::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+                }
+            }
+            dd_grid_wait();
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 DD_ITEM_COORDS(item)
                 for (int i = 0; i < n_kblocks; ++i, ++it) {
                     const int s = it % C::STAGES;
-                    const uint32_t phase = (it / C::STAGES) & 1;
-                    if (!tc::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
                     uint8_t* b_dst = a_dst + C::A_BYTES;
+                    if ((int)it < ahead) {                 // the weight tile of this stage is already on its way
+                        tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+                        continue;
+                    }
+                    const uint32_t phase = (it / C::STAGES) & 1;
+                    if (!tc::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     tc::mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
                     tc::tma_load_2d(a_dst, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
                     tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
@@ -185,6 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. 32*(w%4)+31
+        dd_grid_wait();              // bias is constant, but residual, workspace and counters are earlier kernels' data
         const int quarter = warp & 3;
         uint32_t local = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++local) {
@@ -334,7 +353,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cu
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    gemm_tcgen05_kernel<BN><<<items < sm_count ? items : sm_count, THREADS, C::SMEM_BYTES, s>>>(mw, mx, p);
+    dd_launch(gemm_tcgen05_kernel<BN>, dim3(items < sm_count ? items : sm_count), dim3(THREADS), C::SMEM_BYTES, s, mw, mx, p);
     return dd_check_launch("dd_gemm_tcgen05");
 }
 

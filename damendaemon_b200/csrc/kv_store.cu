@@ -11,6 +11,8 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
                                 const int* __restrict__ block_table, int max_blocks,
                                 T* __restrict__ cache, int n_pages, int kv_heads, int page_size, int head_dim,
                                 int* __restrict__ error_flag) {
+    dd_launch_dependents();
+    dd_grid_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int block = pos / page_size;
@@ -42,10 +44,10 @@ DD_API int dd_kv_store(const void* k_src, const void* v_src, int src_stride, con
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = kv_heads * head_dim >= 1024 ? 256 : 128;
     if (dtype == DD_F32)
-        kv_store_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)k_src, (const float*)v_src, src_stride,
+        dd_launch(kv_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)k_src, (const float*)v_src, src_stride,
             tok_entry, tok_pos, block_table, max_blocks, (float*)cache, n_pages, kv_heads, page_size, head_dim, error_flag);
     else if (dtype == DD_BF16)
-        kv_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src,
+        dd_launch(kv_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src,
             src_stride, tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)cache, n_pages, kv_heads, page_size,
             head_dim, error_flag);
     else

@@ -22,6 +22,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
                                  TO* __restrict__ out, int width, float eps) {
     __shared__ float scratch[THREADS / 32];
+    dd_launch_dependents();
+    dd_grid_wait();
     const int row = blockIdx.x;
     const float* in = x + (size_t)(row_index ? row_index[row] : row) * width;
     float sum = 0.f;
@@ -48,9 +50,9 @@ DD_API int dd_layernorm(const float* x, const int* row_index, const float* gamma
     if (width <= 0) return dd_fail("dd_layernorm: bad width %d", width);
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == DD_F32)
-        layernorm_kernel<float, 256><<<rows, 256, 0, s>>>(x, row_index, gamma, beta, (float*)out, width, eps);
+        dd_launch(layernorm_kernel<float, 256>, dim3(rows), dim3(256), 0, s, x, row_index, gamma, beta, (float*)out, width, eps);
     else if (out_dtype == DD_BF16)
-        layernorm_kernel<__nv_bfloat16, 256><<<rows, 256, 0, s>>>(x, row_index, gamma, beta,
+        dd_launch(layernorm_kernel<__nv_bfloat16, 256>, dim3(rows), dim3(256), 0, s, x, row_index, gamma, beta,
                                                                   (__nv_bfloat16*)out, width, eps);
     else
         return dd_fail("dd_layernorm: unknown output dtype %d", out_dtype);

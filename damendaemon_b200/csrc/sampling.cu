@@ -79,6 +79,8 @@ sample_kernel(const float* __restrict__ logits, int ldl, int V, const float* __r
     __shared__ double sh_d[THREADS / 32];
     __shared__ double prefix[THREADS];
     __shared__ int sh_found;
+    dd_launch_dependents();
+    dd_grid_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ldl;
     bool nan;
@@ -158,6 +160,8 @@ __global__ void adjust_kernel(float* __restrict__ logits, int ldl, int V, const 
                               const float* __restrict__ item_bias, const int* __restrict__ item_seen,
                               const float* __restrict__ repetition, const float* __restrict__ frequency,
                               const float* __restrict__ presence, int n_items) {
+    dd_launch_dependents();
+    dd_grid_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_items) return;
     const int r = item_row[i], t = item_token[i];
@@ -178,7 +182,7 @@ DD_API int dd_sample(const float* logits, int ldl, int rows, int V, const float*
                      const float* top_p, const double* uniform, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (V <= 0) return dd_fail("dd_sample: empty vocabulary");
-    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ldl, V, temperature, top_k, top_p, uniform, out);
+    dd_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, ldl, V, temperature, top_k, top_p, uniform, out);
     return dd_check_launch("dd_sample");
 }
 
@@ -190,7 +194,7 @@ DD_API int dd_adjust_logits(float* logits, int ldl, int V, const int* item_row, 
                             const float* repetition, const float* frequency, const float* presence, int n_items,
                             void* stream) {
     if (n_items <= 0) return 0;
-    adjust_kernel<<<dd_ceil_div(n_items, 256), 256, 0, (cudaStream_t)stream>>>(
+    dd_launch(adjust_kernel, dim3(dd_ceil_div(n_items, 256)), dim3(256), 0, (cudaStream_t)stream, 
         logits, ldl, V, item_row, item_token, item_count, item_bias, item_seen, repetition, frequency, presence, n_items);
     return dd_check_launch("dd_adjust_logits");
 }

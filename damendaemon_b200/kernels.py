@@ -66,6 +66,8 @@ def library(name):
             raise KernelError(f"the '{name}' CUDA kernels are not available ({error}); "
                               "this engine has no CPU or library fallback") from error
         lib.dd_last_error.restype = ctypes.c_char_p
+        lib.dd_set_pdl.argtypes, lib.dd_set_pdl.restype = [_c_int], _c_int
+        lib.dd_set_pdl(1 if _pdl else 0)
         for fn, args in _SIGNATURES[name].items():
             f = getattr(lib, fn)
             f.argtypes, f.restype = args, _c_int
@@ -74,6 +76,17 @@ def library(name):
 
 
 launches = 0          # kernels launched through this module (what the bench reports as gpu_launches)
+
+
+def set_pdl(enabled):
+    """Programmatic dependent launch for every kernel of both libraries (on by default)."""
+    for name in list(_libs):
+        _libs[name].dd_set_pdl(1 if enabled else 0)
+    global _pdl
+    _pdl = bool(enabled)
+
+
+_pdl = True
 
 
 def _call(lib, fn, *args, n_kernels=1):
