@@ -37,15 +37,21 @@ class StepContext:
         want = -(-(self.sm_count * blocks_per_sm) // max(1, self.n_tokens * n_heads))
         return max(1, min(want, (self.split_context + keys_per_block - 1) // keys_per_block, 32))
 
-    def attention(self, q, kv, table, n_heads, scale, window=None):
-        """Paged causal attention of this step's tokens over the cache."""
+    def attend(self, q, k, v, cache, n_heads, scale, window=None):
+        """Put this step's keys and values into the layer's cache pages (unless the cache is another
+        stop's, ``cache.writable == False``) and run paged causal attention of the step's tokens.
+        q, k, v: row views [N, heads * head_dim] of one buffer (the fused projection's output)."""
+        kv, table = cache.kv, self.block_table(cache.group)
         kv_heads, head_dim = kv.shape[2], kv.shape[4]
-        if self.decode_only and self.runtime.attention != "rows" and \
-                kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
+        fast = self.runtime.attention != "rows"
+        if self.decode_only and fast and kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
+            # the decode kernel takes the new keys and values from the projection and writes them itself
             return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
-                                            n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=4))
-        if not self.decode_only and self.runtime.attention != "rows" and \
-                kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
+                                            n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=2),
+                                            k_new=k if cache.writable else None, v_new=v if cache.writable else None)
+        if cache.writable:
+            kernels.kv_store(k, v, self.token_entry, self.positions, table, kv)
+        if not self.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
             return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                       n_splits=self.key_splits(n_heads))

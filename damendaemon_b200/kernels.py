@@ -41,8 +41,8 @@ _SIGNATURES = {
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void],
-        "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void,
-                                _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
+        "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
+                                _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 7
                            + [_c_void, _c_void, _c_int, _c_void, _c_void],
     },
@@ -313,13 +313,21 @@ def attention_decode_supported(n_heads, kv_heads, head_dim, dtype):
     return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_decode_supported(n_heads, kv_heads, head_dim, BF16))
 
 
-def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None):
-    """Decode attention (one query per token) over a bfloat16 cache; see attention_decode_supported."""
+def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
+                     k_new=None, v_new=None):
+    """Decode attention (one query per token) over a bfloat16 cache; see attention_decode_supported.
+    With k_new/v_new (row views of the buffer q lives in) the step's own keys and values are used
+    from there and written into the cache by this kernel; otherwise they must be in the cache already."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n = q.shape[0]
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
             or not cache.is_contiguous():
         raise KernelError("attention_decode: q does not fit the cache")
+    if (k_new is None) != (v_new is None):
+        raise KernelError("attention_decode: k_new and v_new come together")
+    if k_new is not None and (k_new.stride(0) != q.stride(0) or v_new.stride(0) != q.stride(0) or k_new.stride(1) != 1
+                              or v_new.stride(1) != 1 or k_new.dtype != q.dtype or k_new.shape != q.shape):
+        raise KernelError("attention_decode: k_new and v_new must be row views like q")
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
     part_o = part_ml = counters = None
@@ -327,8 +335,8 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
         part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
         counters = _tile_counters(q.device, n * n_heads)
-    _call(library("tensor"), "dd_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
-          _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
+    _call(library("tensor"), "dd_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(k_new, "k_new"), _ptr(v_new, "v_new"),
+          _ptr(cache, "cache"), _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), _ptr(counters), n, n_heads, kv_heads, head_dim, page_size, n_pages,
           0 if window is None else int(window), float(scale), int(n_splits), _ptr(error_flag(q.device)), _stream())

@@ -7,7 +7,6 @@ earlier portions exactly as a decoded token sees its context.
 """
 from __future__ import annotations
 
-from .. import kernels
 from ..cache.manager import PagedKeyValues
 from .interfaces import Mixer
 from .linear import linear
@@ -56,9 +55,6 @@ class Attention(Mixer):
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
         q, k = position.on_query_key(q, k, ctx)
-        table = ctx.block_table(cache.group)
-        if cache.writable:
-            kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, cache.kv)
-        attended = ctx.attention(q, cache.kv, table, s.n_heads, s.scale, s.window)
+        attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)

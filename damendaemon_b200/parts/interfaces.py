@@ -4,7 +4,9 @@
 ``weights``  {checkpoint name: device tensor}, already checked and placed.
 ``runtime``  a ``Runtime`` (below): engine dtype, device and kernel choices.
 ``ctx``      the step's ``StepContext`` (engine/context.py): flattened token metadata
-             on the device, block tables per cache group, scratch.
+             on the device, block tables per cache group, and ``ctx.attend(q, k, v, cache,
+             heads, scale, window)``: cache write plus paged causal attention with the best
+             kernel for the step.
 ``cache``    a ``LayerCache`` (cache/manager.py): ``kv`` pages of this layer
              [pages, 2, kv_heads, page_size, head_dim], ``group`` (its block table is
              ``ctx.block_table(cache.group)``), ``state`` rows [max_requests, ...],

@@ -133,7 +133,7 @@ def paged_case(K, dtype, n_heads, kv_heads, d, page, lengths, new, window, n_spl
     pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
     table = table.to(DEV)
     K.kv_store(kv_, vv_, ent, pos, table, cache)
-    return dict(q=qv, cache=cache, ent=ent, pos=pos, table=table, ref=torch.cat(refs), scale=scale)
+    return dict(q=qv, cache=cache, ent=ent, pos=pos, table=table, ref=torch.cat(refs), scale=scale, packed=packed)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -176,6 +176,19 @@ def test_attention_decode_bf16(K, d, heads, page, n_splits, window):
     assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
     assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
     assert torch.equal(out, again), "the split counters were not left at zero"
+    # fused cache write: wipe the newest key and value from the pages, hand them over beside q
+    packed = c["packed"]
+    hd = heads * d
+    wiped = c["cache"].clone()
+    for e, (L, n) in enumerate(zip([300, 33, 1, 1000, 129], [1] * 5)):
+        pg = int(c["table"][e, (L - 1) // page])
+        wiped[pg, :, :, (L - 1) % page] = float("nan")
+    fused = K.attention_decode(packed[:, :hd], wiped, c["ent"], c["pos"], c["table"], heads, c["scale"], window,
+                               n_splits=n_splits, k_new=packed[:, hd:2 * hd], v_new=packed[:, 2 * hd:])
+    assert K.read_error_flag(DEV) == 0
+    assert torch.equal(fused, out)
+    same = (wiped == c["cache"]) | (torch.isnan(wiped.float()) & torch.isnan(c["cache"].float()))
+    assert bool(same.all()), "the fused kernel did not write the new key and value into the cache"
 
 
 @pytest.mark.parametrize("d,heads,kv_heads,page", [(64, 5, 5, 16), (128, 4, 2, 8), (64, 6, 1, 32)])
