@@ -44,7 +44,12 @@ struct GemmParams {
     int ldr, ldo;
     int act, out_dtype;
     int splits, kblocks_per_split;
+    const uint8_t* prefetch;        // null, or memory a later kernel will stream (the next weight matrix):
+    unsigned long long prefetch_bytes;   // every block asks L2 to fetch its share while this kernel runs
+    unsigned long long* timeline;   // null, or 8 time stamps (ns) per block for looking at where a block's time goes
 };
+
+unsigned long long* g_timeline = nullptr;
 
 template <int BN> struct Config {
     static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
@@ -59,6 +64,31 @@ template <int BN> struct Config {
 // Epilogue of 16 consecutive tokens (m_first ..) of one output feature n. The residual may be
 // the output itself, so all 16 residual values are read before anything is written: the loads
 // stay independent instead of being ordered behind each store.
+// The cluster variant keeps a reduce buffer of (BM + 8) x BN floats beside the stages.
+template <int BN> struct ClusterConfig {
+    // deep rings: with 5 stages (two blocks per SM, so that the next kernel's blocks could prefetch beside this
+    // kernel's) every size measured 15-40% slower than with one block per SM and 8 stages
+    static constexpr int STAGES = BN >= 64 ? 6 : 8;
+    static constexpr int STAGE_BYTES = Config<BN>::STAGE_BYTES;
+    static constexpr int A_BYTES = Config<BN>::A_BYTES;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int REDUCE_BYTES = (BM + 8) * BN * 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + REDUCE_BYTES;
+};
+
+// Ask L2 to fetch this block's share of p.prefetch (16-byte granules, 32 KB per request).
+__device__ __forceinline__ void prefetch_share(const GemmParams& p) {
+    if (!p.prefetch_bytes) return;
+    const unsigned long long share = ((p.prefetch_bytes + gridDim.x - 1) / gridDim.x + 127) & ~127ull;
+    const unsigned long long begin = (unsigned long long)blockIdx.x * share;
+    if (begin >= p.prefetch_bytes) return;
+    const unsigned long long end = min(p.prefetch_bytes, begin + share) & ~15ull;
+    for (unsigned long long at = begin; at < end; at += 32768) {
+        const unsigned n = (unsigned)min(32768ull, end - at);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + at), "r"(n) : "memory");
+    }
+}
+
 __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc) {
     const float b = p.bias ? p.bias[n] : 0.f;
     float r[16];
@@ -151,6 +181,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     tc::tma_load_2d(tiles + i * C::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
                 }
             }
+            prefetch_share(p);
             dd_grid_wait();
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 DD_ITEM_COORDS(item)
@@ -305,6 +336,175 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
+// Split-K inside a thread-block cluster, for a handful of tokens: the S blocks of a cluster share one
+// output tile and each streams 1/S of K, so that ~150 blocks pull a weight matrix that has only a few
+// dozen tiles, and with at most STAGES k-blocks per block the whole weight slice is requested before
+// the preceding kernel has even finished. The partial tiles are reduced over distributed shared
+// memory: block r owns every S-th slice of the tile's 128 features; each block writes, for every
+// feature, its partial row of BN tokens into the owner's shared memory (st.shared::cluster), one
+// cluster barrier later the owner adds the S partials in rank order (deterministic) and applies the
+// epilogue. No global workspace, no counters, no second pass through L2.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                            const GemmParams p) {
+    using C = ClusterConfig<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + C::STAGES;
+    uint64_t* tmem_full_bar = empty_bar + C::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // partial tiles sent to this block: [source rank][BN tokens][features of my slice]; neighbouring threads hold
+    // neighbouring features, so both the remote writes and the reads below walk consecutive banks
+    float* reduce_buf = reinterpret_cast<float*>(tiles + C::STAGES * C::STAGE_BYTES + 256);
+
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 0] = tc::global_ns();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = (int)tc::cluster_size();
+    const int rank = (int)tc::cluster_rank();
+    const int slice = (BM + S - 1) / S;                   // features each block reduces
+    const int tiles_n = (p.N + BM - 1) / BM;
+    const int tile = blockIdx.x / S;
+    const int n0 = (tile % tiles_n) * BM;
+    const int m0 = (tile / tiles_n) * BN;
+    const int total_kblocks = (p.K + BK - 1) / BK;
+    const int kb_begin = rank * p.kblocks_per_split;
+    const int n_kblocks = max(0, min(total_kblocks, kb_begin + p.kblocks_per_split) - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        tc::mbar_init(tmem_full_bar, 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 1] = tc::global_ns();
+    dd_launch_dependents();
+    tc::cluster_arrive();        // "my shared memory exists": waited for before the first remote write
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::prefetch_tensormap(&map_w);
+            tc::prefetch_tensormap(&map_x);
+            // weights first: they do not depend on the kernel before this one
+            const int ahead = min(n_kblocks, C::STAGES);
+            for (int i = 0; i < ahead; ++i) {
+                tc::mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+                tc::tma_load_2d(tiles + i * C::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+            }
+            prefetch_share(p);
+            dd_grid_wait();
+            if (p.timeline) p.timeline[blockIdx.x * 8 + 2] = tc::global_ns();
+            for (int i = 0; i < n_kblocks; ++i) {
+                const int s = i % C::STAGES;
+                uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
+                uint8_t* b_dst = a_dst + C::A_BYTES;
+                if (i < ahead) {
+                    tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+                    continue;
+                }
+                const uint32_t phase = (i / C::STAGES) & 1;
+                if (!tc::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) break;
+                tc::mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+                tc::tma_load_2d(a_dst, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+                tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kblocks; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t phase = (i / C::STAGES) & 1;
+                if (!tc::mbar_wait(&full_bar[s], phase, abort_flag)) { ok = false; break; }
+                if (p.timeline && i == 0) p.timeline[blockIdx.x * 8 + 3] = tc::global_ns();
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles + s * C::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = tc::smem_desc_sw128(a_addr + k * UMMA_K * 2);
+                    const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
+                    tc::mma_bf16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::mma_commit(&empty_bar[s]);
+            }
+            if (p.timeline) p.timeline[blockIdx.x * 8 + 4] = tc::global_ns();
+            if (ok) tc::mma_commit(tmem_full_bar);
+        }
+    }
+    __syncwarp();
+    tc::cluster_wait();          // every block of the cluster is up: remote shared memory may be written
+
+    if (warp >= 2) {
+        const int quarter = warp & 3;
+        const int f = quarter * 32 + lane;                // feature of the tile this thread holds in TMEM
+        const bool have = n_kblocks > 0 && tc::mbar_wait(tmem_full_bar, 0, abort_flag);
+        tc::fence_after_sync();
+        if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 5] = tc::global_ns();
+        const int owner = f / slice, lf = f - owner * slice;
+        // my partial row of feature f goes to the block that owns f
+        const uint32_t remote = tc::map_to_rank(reduce_buf + (size_t)rank * BN * slice + lf, (uint32_t)owner);
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            if (have) { tc::tmem_ld_x16(lane_addr + c0, r); tc::tmem_ld_wait(); }
+            else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0;    // a block without k-blocks (or one that gave up) adds zeros
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) tc::st_cluster_f32(remote + (uint32_t)((c0 + j) * slice) * 4, __uint_as_float(r[j]));
+        }
+    }
+    __syncwarp();
+    tc::cluster_arrive();
+    tc::cluster_wait();          // all partial rows have landed
+    if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 6] = tc::global_ns();
+
+    if (warp >= 2) {
+        dd_grid_wait();          // residual is an earlier kernel's data
+        const int tid = threadIdx.x - 64;                 // 0..127
+        const int first_feature = rank * slice;
+        const int my_features = max(0, min(slice, BM - first_feature));
+        for (int idx = tid; idx < my_features * BN; idx += 128) {
+            const int lf = idx % my_features, tok = idx / my_features;     // neighbouring threads, neighbouring features
+            const int n = n0 + first_feature + lf, m = m0 + tok;
+            if (n >= p.N || m >= p.M) continue;
+            float v = 0.f;
+            for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
+            if (p.bias) v += p.bias[n];
+            v = dd_activation(v, p.act);
+            if (p.residual) v += p.residual[(size_t)m * p.ldr + n];
+            if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 7] = tc::global_ns();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 8);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -357,35 +557,75 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cu
     return dd_check_launch("dd_gemm_tcgen05");
 }
 
+template <int BN>
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t s) {
+    using C = ClusterConfig<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tiles = dd_ceil_div(p.N, BM) * dd_ceil_div(p.M, BN);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(tiles * p.splits);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = s;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = p.splits;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attrs;
+    config.numAttrs = dd_pdl_enabled ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_cluster_kernel<BN>, mw, mx, p);
+    if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05 (cluster of %d): %s", p.splits, cudaGetErrorString(e));
+    return dd_check_launch("dd_gemm_tcgen05");
+}
+
 }  // namespace
 
-// Chooses the token tile and the K split for a problem; also tells the caller how much workspace it needs.
-// Returns splits (>= 1); *token_tile gets BN.
-DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile) {
+// Debugging aid: a device buffer of 8 * blocks time stamps that the cluster kernel fills (null switches it off).
+DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
+
+// Chooses the token tile, the K split and how the split is reduced (*cluster = 1: inside a thread-block
+// cluster over distributed shared memory; 0: through a global workspace). Returns splits (>= 1).
+DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile, int* cluster) {
     // 128 tokens per tile above 64: measured equal or better than 256 at 2,048 and 4,096 tokens (more tiles to balance)
     int bn = 128;
     if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64;
     if (token_tile) *token_tile = bn;
+    if (cluster) *cluster = 0;
     const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
     const int kblocks = dd_ceil_div(K, BK);
-    // Splitting K costs a round trip through the workspace (a few microseconds of latency), so it pays only
-    // when few CTAs would each stream a long K: a handful of tokens, few tiles, at least 64 k-blocks.
+    // A step of a few tokens has a few dozen tiles at most: split K inside clusters so that about as many
+    // blocks as there are SMs stream the weights, all in one wave (a cluster must be resident as a whole).
+    // Above 32 tokens the reduction of a wide tile costs more than the split saves unless the tiles are very few
+    // (measured at 64 tokens: 4800 and 6400 features faster unsplit, 1600 features faster split).
     int splits = 1;
-    if (M <= 16 && kblocks >= 64 && tiles * 4 < sm_count) {
-        splits = dd_ceil_div(sm_count, 2 * tiles);
+    if (M <= 64 && tiles * 2 <= sm_count && (M <= 32 || tiles <= 16)) {
+        splits = sm_count / tiles;
         if (splits > 8) splits = 8;
+        if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
+        if (splits > 1 && cluster) *cluster = 1;
     }
     return splits;
 }
 
 // X [M,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw); bias [N] f32 or null; residual [M,N] f32
-// (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). workspace: f32
-// [splits*M*N] and counters: int32 [tiles], zero before the first launch (both only when splits > 1).
+// (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). cluster = 1: splits
+// (at most 8) are the blocks of a cluster and reduce over distributed shared memory (token_tile <= 64);
+// cluster = 0 with splits > 1: workspace f32 [splits*M*N] and counters int32 [tiles], zero before the
+// first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
+// weight matrix of a decode step): this kernel's blocks ask L2 to fetch it while they run.
 DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const float* bias, const float* residual,
                            int ldr, void* out, int ldo, int M, int N, int K, int act, int out_dtype, int splits,
-                           int token_tile, float* workspace, int* counters, int n_counters, int* error_flag,
-                           void* stream) {
+                           int token_tile, int cluster, float* workspace, int* counters, int n_counters,
+                           const void* prefetch, long long prefetch_bytes, int* error_flag, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
         return dd_fail("dd_gemm_tcgen05: K=%d and the row strides (%d, %d) must be multiples of 8 (TMA needs 16-byte rows)", K, ldx, ldw);
@@ -393,12 +633,18 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     if (out_dtype != DD_BF16 && out_dtype != DD_F32) return dd_fail("dd_gemm_tcgen05: unknown output dtype %d", out_dtype);
     const int kblocks = dd_ceil_div(K, BK);
     if (splits < 1 || splits > kblocks) return dd_fail("dd_gemm_tcgen05: bad split count %d for %d k-blocks", splits, kblocks);
+    if (cluster && (splits > 8 || token_tile > 64))
+        return dd_fail("dd_gemm_tcgen05: a cluster has at most 8 blocks and a token tile of at most 64 (got %d, %d)", splits, token_tile);
     GemmParams p;
     p.bias = bias; p.residual = residual; p.out = out; p.workspace = workspace; p.counters = counters;
     p.error_flag = error_flag; p.M = M; p.N = N; p.K = K; p.ldr = ldr; p.ldo = ldo; p.act = act; p.out_dtype = out_dtype;
+    p.timeline = g_timeline;
+    p.prefetch = (const uint8_t*)prefetch;
+    p.prefetch_bytes = (prefetch && prefetch_bytes > 0 && !((uintptr_t)prefetch & 15)) ? (unsigned long long)prefetch_bytes : 0;
     p.splits = splits; p.kblocks_per_split = dd_ceil_div(kblocks, splits);
     p.splits = dd_ceil_div(kblocks, p.kblocks_per_split);     // no empty split
-    if (p.splits > 1) {
+    if (p.splits == 1) cluster = 0;
+    if (p.splits > 1 && !cluster) {
         const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, token_tile);
         if (!workspace || !counters || n_counters < tiles)
             return dd_fail("dd_gemm_tcgen05: split-K needs a workspace and %d counters", tiles);
@@ -407,6 +653,14 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     if (int e = make_map(&mw, W, N, K, ldw, BM, "the weight matrix")) return e;
     if (int e = make_map(&mx, X, M, K, ldx, token_tile, "the activations")) return e;
     cudaStream_t s = (cudaStream_t)stream;
+    if (cluster) {
+        switch (token_tile) {
+            case 16: return launch_cluster<16>(mw, mx, p, s);
+            case 32: return launch_cluster<32>(mw, mx, p, s);
+            case 64: return launch_cluster<64>(mw, mx, p, s);
+        }
+        return dd_fail("dd_gemm_tcgen05: token tile %d is not one of 16, 32, 64 for a cluster", token_tile);
+    }
     switch (token_tile) {
         case 16: return launch<16>(mw, mx, p, s);
         case 32: return launch<32>(mw, mx, p, s);

@@ -36,15 +36,15 @@ _SIGNATURES = {
         "dd_adjust_logits": [_c_void, _c_int, _c_int] + [_c_void] * 8 + [_c_int, _c_void],
     },
     "tensor": {
-        "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void],
         "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
                                 _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
-        "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 7
-                           + [_c_void, _c_void, _c_int, _c_void, _c_void],
+        "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 8
+                           + [_c_void, _c_void, _c_int, _c_void, ctypes.c_longlong, _c_void, _c_void],
     },
 }
 
@@ -278,9 +278,16 @@ def sm_count(device):
     return _sm_count[key]
 
 
-def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None, splits=None, token_tile=None):
+_plans = {}
+
+
+def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None, splits=None, token_tile=None,
+                 cluster=None, prefetch=None):
     """act(a @ w.T + bias) (+ residual) on the tcgen05 tensor cores. a [M,K] and w [N,K] bfloat16,
-    bias/residual float32, out bfloat16 or float32. K and the row strides must be multiples of 8."""
+    bias/residual float32, out bfloat16 or float32. K and the row strides must be multiples of 8.
+    splits/token_tile/cluster override the kernel's own plan (cluster: reduce the K splits inside a
+    thread-block cluster instead of through a workspace). prefetch: a tensor that a later kernel will
+    stream (the next weight matrix of a decode step); this kernel asks L2 to fetch it meanwhile."""
     _rows(a, "a"), _rows(w, "w")
     M, K = a.shape
     N = w.shape[0]
@@ -291,21 +298,28 @@ def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     _rows(out, "out")
     lib = library("tensor")
-    tile = ctypes.c_int(0)
-    planned = lib.dd_gemm_tcgen05_plan(M, N, K, sm_count(a.device), ctypes.byref(tile))
-    splits = planned if splits is None else splits
-    token_tile = tile.value if token_tile is None else token_tile
+    plan = _plans.get((M, N, K))
+    if plan is None:
+        tile, mode = ctypes.c_int(0), ctypes.c_int(0)
+        planned = lib.dd_gemm_tcgen05_plan(M, N, K, sm_count(a.device), ctypes.byref(tile), ctypes.byref(mode))
+        plan = _plans[(M, N, K)] = (planned, tile.value, mode.value)
+    if splits is not None and cluster is None:
+        cluster = 0
+    splits = plan[0] if splits is None else splits
+    token_tile = plan[1] if token_tile is None else token_tile
+    cluster = plan[2] if cluster is None else int(cluster)
     workspace = counters = None
     n_counters = 0
-    if splits > 1:
+    if splits > 1 and not cluster:
         workspace = torch.empty((splits * M * N,), dtype=torch.float32, device=a.device)
         n_counters = ((N + 127) // 128) * ((M + token_tile - 1) // token_tile)
         counters = _tile_counters(a.device, n_counters)
     _call(lib, "dd_gemm_tcgen05", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(0),
           _ptr(bias, "bias", torch.float32), _ptr(residual, "residual", torch.float32),
           0 if residual is None else residual.stride(0), _ptr(out, "out", out_dtype), out.stride(0), M, N, K,
-          ACTIVATIONS[activation], _dt(out_dtype), splits, token_tile, _ptr(workspace), _ptr(counters), n_counters,
-          _ptr(error_flag(a.device)), _stream())
+          ACTIVATIONS[activation], _dt(out_dtype), splits, token_tile, cluster, _ptr(workspace), _ptr(counters), n_counters,
+          None if prefetch is None else prefetch.data_ptr(),
+          0 if prefetch is None else prefetch.numel() * prefetch.element_size(), _ptr(error_flag(a.device)), _stream())
     return out
 
 

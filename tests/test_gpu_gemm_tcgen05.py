@@ -68,6 +68,26 @@ def test_forced_splits_and_tiles(K, splits, tile):
     assert torch.equal(out, again), "split-K sums in a fixed order: two runs are bit-equal"
 
 
+@pytest.mark.parametrize("splits", [2, 3, 5, 8])
+@pytest.mark.parametrize("tokens,tile", [(1, 16), (8, 16), (13, 16), (30, 32), (64, 64)])
+def test_cluster_split(K, splits, tokens, tile):
+    """K split inside a thread-block cluster, partial tiles reduced over distributed shared memory."""
+    a, w, bias, res = operands(tokens, 700, 1600, seed=4)
+    ref = a.double() @ w.double().t() + bias.double()
+    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=1)
+    again = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=1)
+    assert K.read_error_flag(DEV) == 0
+    assert (out.double() - ref).abs().max() < 1e-3
+    assert torch.equal(out, again), "the partial tiles are added in rank order: two runs are bit-equal"
+    stream = res.clone()
+    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream, splits=splits, token_tile=tile, cluster=1)
+    assert (stream.double() - (ref + res.double())).abs().max() < 1e-3
+    gelu = K.gemm_tcgen05(a, w, bias, activation="gelu_new", splits=splits, token_tile=tile, cluster=1)
+    u = ref
+    want = 0.5 * u * (1 + torch.tanh(math.sqrt(2 / math.pi) * (u + 0.044715 * u ** 3)))
+    assert (gelu.double() - want).abs().max() < 2.0 ** -8 * float(want.abs().max()) + 1e-3
+
+
 def test_strided_views_and_refusals(K):
     a, w, bias, res = operands(20, 256, 128, seed=3)
     wide = torch.zeros(20, 128 + 64, dtype=torch.bfloat16, device=DEV)
