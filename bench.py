@@ -209,7 +209,10 @@ def reference_arm(args):
         try:
             sys.path.insert(0, str(ROOT / "baseline"))
             import run_reference
-            print(json.dumps(run_reference.run(args, XL, PROMPT)), flush=True)
+            config = dict(XL)
+            if args.layers:
+                config["n_layer"] = args.layers
+            print(json.dumps(run_reference.run(args, config, PROMPT)), flush=True)
             return 0
         except Exception as error:      # noqa: BLE001
             why = f"the reference arm failed: {type(error).__name__}: {str(error)[:200]}"

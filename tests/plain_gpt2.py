@@ -109,7 +109,7 @@ def mlp_block(x, w, prefix, activation):
     return conv1d(g, w[prefix + "mlp.c_proj.weight"], w[prefix + "mlp.c_proj.bias"])
 
 
-def logits_of(config, w, ids, rounded=None):
+def logits_of(config, w, ids, rounded=None, rows=None):
     """Logits at every position of one whole sequence, [T, vocab]  (damendaemon/gpt2.py:42-66).
 
     ``rounded``: a dtype (torch.bfloat16) to which the activations that a reduced-precision engine
@@ -138,6 +138,8 @@ def logits_of(config, w, ids, rounded=None):
         u = conv1d(y, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"])
         g = keep(gelu_new(u) if activation == "gelu_new" else gelu_erf(u))
         x = x + conv1d(g, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]       # the head only where it is asked for (damendaemon/gpt2.py:65)
     x = keep(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps))
     return x @ w["wte.weight"].t()          # tied head, no bias (damendaemon/gpt2.py:18,66)
 
@@ -146,8 +148,8 @@ class PlainGpt2:
     def __init__(self, folder, dtype=torch.float64):
         self.config, self.w = read_folder(folder, dtype)
 
-    def logits(self, ids, rounded=None):
-        return logits_of(self.config, self.w, ids, rounded)
+    def logits(self, ids, rounded=None, rows=None):
+        return logits_of(self.config, self.w, ids, rounded, rows)
 
     def greedy(self, prompt, n_new):
         ids = list(prompt)
