@@ -27,6 +27,16 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
     T* v_dst = k_dst + plane;
     const T* ks = k_src + (size_t)t * src_stride;
     const T* vs = v_src + (size_t)t * src_stride;
+    constexpr int V = 16 / sizeof(T);       // elements per 16-byte copy
+    if (head_dim % V == 0 && src_stride % V == 0 && (((uintptr_t)k_src | (uintptr_t)v_src | (uintptr_t)cache) & 15) == 0) {
+        for (int c = threadIdx.x * V; c < row; c += blockDim.x * V) {
+            const int h = c / head_dim, i = c - h * head_dim;
+            const size_t off = (size_t)h * page_size * head_dim + i;
+            *reinterpret_cast<uint4*>(k_dst + off) = *reinterpret_cast<const uint4*>(ks + c);
+            *reinterpret_cast<uint4*>(v_dst + off) = *reinterpret_cast<const uint4*>(vs + c);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < row; c += blockDim.x) {
         const int h = c / head_dim, i = c - h * head_dim;
         const size_t off = (size_t)h * page_size * head_dim + i;

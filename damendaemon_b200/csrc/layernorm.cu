@@ -75,11 +75,81 @@ layernorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
     }
 }
 
+// Rows whose width is a multiple of 4 and at most 128 * 4 * VPT: 128 threads, the row in registers as
+// float4, 16-byte loads and packed stores. Sixteen such blocks share an SM, so thousands of rows stream.
+template <typename TO> struct Pack4;
+template <> struct Pack4<float> {
+    __device__ static void store(float* dst, float a, float b, float c, float d) { *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d); }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    __device__ static void store(__nv_bfloat16* dst, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t*>(&lo);
+        v.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = v;
+    }
+};
+
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(128)
+layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+                     const float* __restrict__ gamma, const float* __restrict__ beta,
+                     TO* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[4];
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int row = blockIdx.x;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * width);
+    const int n4 = width >> 2;
+    float4 v[VPT];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        v[i] = c < n4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = block_sum<128>(sum, scratch) / (float)width;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (threadIdx.x + i * 128 < n4) {
+            const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            sq += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float rstd = 1.0f / sqrtf(block_sum<128>(sq, scratch) / (float)width + eps);
+    TO* o = out + (size_t)row * width;
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        if (c < n4) {
+            const float4 g = g4[c];
+            const float4 b = beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            Pack4<TO>::store(o + 4 * c, (v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
+                             (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+        }
+    }
+}
+
 DD_API int dd_layernorm(const float* x, const int* row_index, const float* gamma, const float* beta,
                         void* out, int rows, int width, float eps, int out_dtype, void* stream) {
     if (rows <= 0) return 0;
     if (width <= 0) return dd_fail("dd_layernorm: bad width %d", width);
     cudaStream_t s = (cudaStream_t)stream;
+    if (width % 4 == 0 && width <= 128 * 4 * 4 && !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)gamma | (uintptr_t)beta) & 15)) {
+        if (out_dtype == DD_F32)
+            dd_launch(layernorm_vec_kernel<float, 4>, dim3(rows), dim3(128), 0, s, x, row_index, gamma, beta, (float*)out, width, eps);
+        else if (out_dtype == DD_BF16)
+            dd_launch(layernorm_vec_kernel<__nv_bfloat16, 4>, dim3(rows), dim3(128), 0, s, x, row_index, gamma, beta,
+                      (__nv_bfloat16*)out, width, eps);
+        else
+            return dd_fail("dd_layernorm: unknown output dtype %d", out_dtype);
+        return dd_check_launch("dd_layernorm");
+    }
     if (out_dtype == DD_F32)
         dd_launch(layernorm_kernel<float, 256, 8>, dim3(rows), dim3(256), 0, s, x, row_index, gamma, beta, (float*)out, width, eps);
     else if (out_dtype == DD_BF16)

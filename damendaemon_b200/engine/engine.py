@@ -86,6 +86,7 @@ class Engine:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_graph = use_graph and self.model.graph_safe
         self._graphs, self._seen = {}, set()
+        self.max_graphs = 48                            # replayable step shapes kept; the least recently used goes first
         kernels.error_flag(self.device)                 # allocated before any graph capture
         if self.dtype == torch.bfloat16 and gemm != "simt":
             heads = max((getattr(l.mixer, "n_heads", 1) for l in self.spec.layers), default=1)
@@ -221,18 +222,23 @@ class Engine:
         decode_only = N == E
         slots, pos0 = self._upload(entries, lengths, at)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
-        if self.use_graph and decode_only and M > 0:
-            key = (E, M)
+        if self.use_graph and M > 0:
+            # Every kernel reads lengths, positions and page tables from the metadata buffer, and launch shapes
+            # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.
+            key = (N, E, M, decode_only)
             graph = self._graphs.get(key)
             if graph is None and key in self._seen:
                 # the second step of this shape: capture it (the first ran eagerly and warmed everything up)
-                ctx = self._context(N, E, M, at, True, self.max_context)
+                ctx = self._context(N, E, M, at, decode_only, self.max_context)
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.current_stream().synchronize()
                 with torch.cuda.graph(graph):
                     static_logits = self.model.forward(ctx, self._caches)
+                while len(self._graphs) >= self.max_graphs:
+                    self._graphs.pop(next(iter(self._graphs)))
                 self._graphs[key] = graph = (graph, static_logits)
             if graph is not None:
+                self._graphs[key] = self._graphs.pop(key)        # most recently used last
                 graph[0].replay()
                 return graph[1]             # valid until the next step of this shape
             self._seen.add(key)
@@ -245,8 +251,8 @@ class Engine:
         the entries and of each entry's ``want`` (an empty [0, vocab] tensor if none are wanted).
         ``end``: requests that are finished after this step; what they hold is given back.
         Raises StepError (bad batch) or PageCapacityError (no pages) with nothing changed.
-        With CUDA graphs on, the logits of a decode-only step live in a buffer that the next
-        step of the same shape overwrites."""
+        With CUDA graphs on, the logits of a step whose counts (tokens, entries, wanted places) were
+        seen before live in a buffer that the next step of the same counts overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         fresh = [e.request for e in entries if e.request not in self.cache.slot_of]
