@@ -198,6 +198,54 @@ def prefill_flops(c, layers, tokens_per_prompt=1024, prompts=2):
     return gemm + attention
 
 
+WORKLOADS = {
+    # GPT-2 medium shape: 32 requests, prompt lengths uniform in [16, 768], 128 new tokens each at temperature 1.0,
+    # admitted continuously
+    "medium": {"config": {**XL, "n_layer": 24, "n_embd": 1024, "n_head": 16, "n_inner": 4096}, "max_live": 32},
+    # GPT-2 large shape: 8 prompts of 1,000 tokens in portions of 256 beside 56 requests that decode from contexts
+    # spread over 1..1000, greedy
+    "large": {"config": {**XL, "n_layer": 36, "n_embd": 1280, "n_head": 20, "n_inner": 5120}, "max_live": 64},
+}
+
+
+def run_workload(name):
+    """The scheduler under a mixed load (continuous batching): total generated tokens per second and the step mix."""
+    import random
+    import torch
+    from damendaemon_b200.engine.scheduler import Request, Scheduler
+    from damendaemon_b200.sampling import Sampling
+    spec = WORKLOADS[name]
+    config = spec["config"]
+    vocab = config["vocab_size"]
+    runtime = make_runtime(config, spec["max_live"])
+    rng = random.Random(0)
+    if name == "medium":
+        scheduler = Scheduler(runtime.engine, token_budget=2048, chunk_size=512, max_live=32)
+        requests = [Request(random_ids(rng.randint(16, 768), vocab, 10 + i), 128, Sampling(temperature=1.0, seed=i), True)
+                    for i in range(32)]
+    else:
+        scheduler = Scheduler(runtime.engine, token_budget=2048, chunk_size=256, max_live=64, length_policy="clamp")
+        requests = [Request(random_ids(1 + (i * 999) // 55, vocab, 10 + i), 24, Sampling(), True) for i in range(56)]
+        requests += [Request(random_ids(1000, vocab, 100 + i), 24, Sampling(), True) for i in range(8)]
+    for r in requests:
+        scheduler.submit(r)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in scheduler.run():
+        pass
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    generated = sum(len(r.output) for r in requests)
+    prompt_tokens = sum(len(r.prompt) for r in requests)
+    mixed = sum(1 for p, d in scheduler.step_log if p and d)
+    return {"workload": name, "metric": "generated tokens/s through the scheduler", "value": round(generated / wall, 1),
+            "unit": "tokens/s", "requests": len(requests), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+            "prompt_tokens_per_s": round(prompt_tokens / wall, 1), "seconds": round(wall, 3), "steps": scheduler.steps,
+            "steps_mixing_prompt_and_decode": mixed, "failed": sum(1 for r in requests if r.finish_reason == "error"),
+            "config": {"n_layer": config["n_layer"], "n_embd": config["n_embd"], "n_head": config["n_head"], "dtype": "bf16",
+                       "note": "first run of each step shape is eager and captures a CUDA graph; no warm-up pass"}}
+
+
 def reference_arm(args):
     """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
     ref = ROOT / "baseline" / "_ref"
@@ -232,12 +280,16 @@ def main():
     parser.add_argument("--no-graph", action="store_true", help="launch every decode kernel eagerly (for profilers)")
     parser.add_argument("--kernel-case", help="time one kernel alone at XL shape (see damendaemon_b200/kernel_cases.py)")
     parser.add_argument("--case-iters", type=int, default=50)
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload:
+        print(json.dumps(run_workload(args.workload)), flush=True)
+        return 0
     if args.kernel_case:
         from damendaemon_b200.kernel_cases import time_case
         print(json.dumps(time_case(args.kernel_case, args.case_iters)), flush=True)

@@ -246,3 +246,13 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, order):
     # a finished request's slot starts from zero state again
     again = engine.step([StepEntry("c", b, list(range(23)))])
     assert (again.cpu() - want["b"]).abs().max() < tol
+
+
+def test_bfloat16_width_that_is_no_multiple_of_8():
+    """A reduction width that TMA cannot take (100 = 4 mod 8) falls to the CUDA-core GEMM, never to a wrong result."""
+    from damendaemon_b200.parts.linear import linear
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(5, 100, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(36, 100, generator=g).to(torch.bfloat16).to(DEV)
+    out = linear(runtime(torch.bfloat16), a, w, out_dtype=torch.float32)
+    assert (out.double() - a.double() @ w.double().t()).abs().max() < 1e-3
