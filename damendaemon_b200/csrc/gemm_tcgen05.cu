@@ -52,14 +52,26 @@ struct GemmParams {
 unsigned long long* g_timeline = nullptr;
 
 template <int BN> struct Config {
-    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 192 ? 4 : (BN >= 128 ? 6 : 8));
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int ACC_COLS = BN < 16 ? 16 : BN;              // columns of one accumulator
+    static constexpr int ACC_COLS = BN == 192 ? 256 : (BN < 16 ? 16 : BN);   // columns of one accumulator (a power of two)
     static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;   // two accumulators, a power of two >= 32
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
+
+// gelu_new for a bfloat16 result: the hardware tanh (tanh.approx.f32, relative error about 2^-11) is below what
+// bfloat16 keeps; with tanhf the epilogue of a 128x128 tile took longer than its MMAs (93 us against 57 us for
+// the 6400-wide projection of 2,048 tokens). float32 outputs and the erf form keep the exact functions.
+__device__ __forceinline__ float activation_for(float u, int act, int out_dtype) {
+    if (act == DD_ACT_GELU_NEW && out_dtype == DD_BF16) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+        return 0.5f * u * (1.0f + t);
+    }
+    return dd_activation(u, act);
+}
 
 // Epilogue of 16 consecutive tokens (m_first ..) of one output feature n. The residual may be
 // the output itself, so all 16 residual values are read before anything is written: the loads
@@ -99,7 +111,7 @@ __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, in
     for (int j = 0; j < 16; ++j) {
         const int m = m_first + j;
         if (m >= p.M) break;
-        const float v = dd_activation(acc[j] + b, p.act) + r[j];
+        const float v = activation_for(acc[j] + b, p.act, p.out_dtype) + r[j];
         if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
         else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
     }
@@ -489,7 +501,7 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
             float v = 0.f;
             for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
             if (p.bias) v += p.bias[n];
-            v = dd_activation(v, p.act);
+            v = activation_for(v, p.act, p.out_dtype);
             if (p.residual) v += p.residual[(size_t)m * p.ldr + n];
             if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
             else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
@@ -594,9 +606,20 @@ DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = 
 // Chooses the token tile, the K split and how the split is reduced (*cluster = 1: inside a thread-block
 // cluster over distributed shared memory; 0: through a global workspace). Returns splits (>= 1).
 DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile, int* cluster) {
-    // 128 tokens per tile above 64: measured equal or better than 256 at 2,048 and 4,096 tokens (more tiles to balance)
+    // Above 64 tokens: the tile among 128, 192 and 256 tokens that needs the least time in whole rounds of one tile
+    // per SM (rounds x tokens per tile); ties go to the smaller tile, which balances better.
     int bn = 128;
     if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64;
+    else {
+        long long best = -1;
+        const int candidates[3] = {128, 192, 256};
+        for (int i = 0; i < 3; ++i) {
+            const int c = candidates[i];
+            const long long t = (long long)dd_ceil_div(N, BM) * dd_ceil_div(M, c);
+            const long long cost = (long long)dd_ceil_div(t, sm_count) * c;
+            if (best < 0 || cost < best) { best = cost; bn = c; }
+        }
+    }
     if (token_tile) *token_tile = bn;
     if (cluster) *cluster = 0;
     const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
@@ -607,7 +630,7 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     // (measured at 64 tokens: 4800 and 6400 features faster unsplit, 1600 features faster split).
     int splits = 1;
     if (M <= 64 && tiles * 2 <= sm_count && (M <= 32 || tiles <= 16)) {
-        splits = sm_count / tiles;
+        splits = sm_count / tiles;       // fewer, so that two kernels' blocks could sit side by side, measured slower
         if (splits > 8) splits = 8;
         if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
@@ -666,7 +689,8 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
         case 32: return launch<32>(mw, mx, p, s);
         case 64: return launch<64>(mw, mx, p, s);
         case 128: return launch<128>(mw, mx, p, s);
+        case 192: return launch<192>(mw, mx, p, s);
         case 256: return launch<256>(mw, mx, p, s);
     }
-    return dd_fail("dd_gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", token_tile);
+    return dd_fail("dd_gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 192, 256", token_tile);
 }
