@@ -34,6 +34,13 @@ TINY_C = {
     "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
     "scale_attn_by_inverse_layer_idx": False,
 }
+# and an awkward one: one layer, five heads of 16, an inner width (100) and a vocabulary (97) that are no multiple of 8
+TINY_D = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 1, "n_embd": 80, "n_head": 5, "n_inner": 100, "vocab_size": 97, "n_positions": 96,
+    "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_by_inverse_layer_idx": True,
+}
 
 
 @pytest.fixture(scope="session")
