@@ -1,14 +1,16 @@
 // Decode attention for bfloat16 caches: one query token per (token, head), keys cut into splits so
 // that a small batch still fills the GPU, the split results merged by the block that finishes last.
 //
-// A block of 4 warps owns (split, head, token). A key row of D bf16 is fetched by D/8 neighbouring
-// lanes, 16 bytes each, so one copy instruction of a warp moves 32/(D/8) consecutive keys (512
-// contiguous bytes of a page). Every warp runs its own ring of cp.async stages in shared memory
-// (16 keys of K and V per stage, three stages deep: 48 KB per block, so four blocks and their 16
-// warps share an SM; with fewer, larger stages the arithmetic's dependency chains were left
-// uncovered and the kernel ran at two thirds of this speed); a lane reads back exactly the chunks
-// it copied itself, which needs no synchronisation beyond cp.async.wait_group. Scores, running maximum, sum and the
-// weighted value sum are float32 in the base-2 domain (q is pre-multiplied by scale * log2 e).
+// A block of 4 warps owns (split, head, token). Every warp runs its own ring of cp.async stages in
+// shared memory (16 keys of K and V per stage, three stages deep: 48 KB per block, so four blocks
+// and their 16 warps share an SM). A key row of D bf16 is fetched by D/8 neighbouring lanes, 16
+// bytes each, into a row-major tile whose 16-byte chunks are swizzled by the key index, so that
+// ldmatrix reads it without bank conflicts. Scores and the weighted value sum run on the tensor
+// cores (mma.sync m16n8k16, float32 accumulate) with the single query in row 0 of the 16-row
+// operand: fifteen rows are idle, but a 16-key stage costs about 55 warp instructions instead of the
+// 175 that unpacking bf16 and scalar FMAs cost, and it is instruction issue, not tensor throughput,
+// that limits this kernel beside the memory system. Running maximum, sum and the softmax are
+// float32 in the base-2 domain.
 //
 // With k_new/v_new given, the step's own key and value (position = the token's position) are taken
 // from there instead of the cache and written to the cache page by the one warp that meets them:
@@ -21,22 +23,36 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int STEPS = 4;            // copy instructions of K (and of V) per lane and stage
+constexpr int TILE = 16;            // keys per stage (one k-step of the P.V product)
 constexpr int STAGES = 3;           // ring depth per warp
 
-__device__ __forceinline__ void unpack8(const uint4& v, float* out) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        out[2 * i] = __uint_as_float(w[i] << 16);
-        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t* r) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of 16-byte chunk c of key row r in a [16][D] tile, chunks swizzled by the row
+template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
+    return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
+}
 
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -47,11 +63,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters, int H, int P, int n_pages, int window, float scale_log2e,
                         int* __restrict__ error_flag) {
-    constexpr int C = D / 8;            // lanes per key row
+    constexpr int C = D / 8;            // 16-byte chunks (and lanes) per key row
     constexpr int KPL = 32 / C;         // keys per copy instruction of a warp
-    constexpr int TILE = KPL * STEPS;   // keys per stage
-    constexpr int STAGE_U4 = 2 * STEPS * 32;      // uint4 per stage: K then V
-    extern __shared__ uint4 ring[];     // [WARPS][STAGES][STAGE_U4]
+    constexpr int STEPS = TILE / KPL;   // copy instructions of K (and of V) per lane and stage
+    constexpr int KS = D / 16;          // k-steps of q.k over the head dimension
+    constexpr int TILE_BYTES = TILE * D * 2;
+    extern __shared__ __align__(128) uint8_t ring[];     // [WARPS][STAGES][K tile, V tile]
     __shared__ float sh_o[WARPS][D];
     __shared__ float sh_ml[WARPS][2];
     __shared__ int sh_last;
@@ -61,6 +78,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int split = blockIdx.x, n_splits = gridDim.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = lane % C, kg = lane / C;
+    const int g = lane >> 2, t4 = lane & 3;
     const int pos = tok_pos[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int hi = pos + 1;
@@ -69,48 +87,52 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int k0 = lo + split * per;
     const int k1 = min(hi, k0 + per);
 
-    float qv[8];
+    // the query as the A operand: row 0 of a 16-row tile, every other row zero
+    uint32_t qf[KS][4];
     {
-        const uint4 raw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * D + c * 8);
-        unpack8(raw, qv);
+        const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * D;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qv[i] *= scale_log2e;
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * t4) : 0u;
+            qf[ks][1] = 0u;
+            qf[ks][2] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + 2 * t4) : 0u;
+            qf[ks][3] = 0u;
+        }
     }
     const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
     const size_t head_plane = (size_t)P * D;
     const size_t page_stride = 2 * (size_t)H * head_plane;       // key/value heads = heads here
     const size_t k_off = (size_t)h * head_plane + c * 8;
     const size_t v_off = k_off + (size_t)H * head_plane;
-    uint4* my_ring = ring + (size_t)warp * STAGES * STAGE_U4;
-    unsigned valid_bits[STAGES];        // per stage: bit i = step i of this lane holds a live key
+    uint8_t* my_ring = ring + (size_t)warp * STAGES * 2 * TILE_BYTES;
 
     // tiles of this warp: base = k0 + (warp + i * WARPS) * TILE
     const int first_key = k0 + warp * TILE;
     const int n_tiles = first_key < k1 ? (k1 - first_key + WARPS * TILE - 1) / (WARPS * TILE) : 0;
     auto issue = [&](int i) {
-        const int stage = i % STAGES;
-        uint4* dst = my_ring + stage * STAGE_U4;
+        uint8_t* kt = my_ring + (i % STAGES) * 2 * TILE_BYTES;
+        uint8_t* vt = kt + TILE_BYTES;
         const int base = first_key + i * WARPS * TILE;
-        unsigned bits = 0;
 #pragma unroll
         for (int s = 0; s < STEPS; ++s) {
-            const int key = base + s * KPL + kg;
+            const int row = s * KPL + kg;
+            const int key = base + row;
+            const uint32_t off = tile_off<D>(row, c);
             bool ok = key < k1;
             if (ok && k_new != nullptr && key == pos) {
                 // this step's own key and value: from the projection's output, and into the cache
                 const __nv_bfloat16* ks = k_new + (size_t)t * q_stride + (size_t)h * D + c * 8;
                 const __nv_bfloat16* vs = v_new + (size_t)t * q_stride + (size_t)h * D + c * 8;
-                cp_async16(dst + s * 32 + lane, ks);
-                cp_async16(dst + STEPS * 32 + s * 32 + lane, vs);
+                cp_async16(kt + off, ks);
+                cp_async16(vt + off, vs);
                 const int blk = key / P;
                 const int page = blk < max_blocks ? bt[blk] : -1;
                 if (page < 0 || page >= n_pages) atomicOr(error_flag, 2);
                 else {
-                    const size_t off = (size_t)page * page_stride + (size_t)(key % P) * D;
-                    *reinterpret_cast<uint4*>(cache + off + k_off) = *reinterpret_cast<const uint4*>(ks);
-                    *reinterpret_cast<uint4*>(cache + off + v_off) = *reinterpret_cast<const uint4*>(vs);
+                    const size_t dst = (size_t)page * page_stride + (size_t)(key % P) * D;
+                    *reinterpret_cast<uint4*>(cache + dst + k_off) = *reinterpret_cast<const uint4*>(ks);
+                    *reinterpret_cast<uint4*>(cache + dst + v_off) = *reinterpret_cast<const uint4*>(vs);
                 }
-                bits |= 1u << s;
                 continue;
             }
             if (ok) {
@@ -120,20 +142,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                     atomicOr(error_flag, 4);
                     ok = false;
                 } else {
-                    const size_t off = (size_t)page * page_stride + (size_t)(key % P) * D;
-                    cp_async16(dst + s * 32 + lane, cache + off + k_off);
-                    cp_async16(dst + STEPS * 32 + s * 32 + lane, cache + off + v_off);
-                    bits |= 1u << s;
+                    const size_t src = (size_t)page * page_stride + (size_t)(key % P) * D;
+                    cp_async16(kt + off, cache + src + k_off);
+                    cp_async16(vt + off, cache + src + v_off);
                 }
             }
-            if (!ok) dst[STEPS * 32 + s * 32 + lane] = make_uint4(0, 0, 0, 0);   // a masked value must be zero, not stale
+            if (!ok) {          // keys beyond the range are masked by their index; their rows must still be finite
+                *reinterpret_cast<uint4*>(kt + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vt + off) = make_uint4(0, 0, 0, 0);
+            }
         }
-        valid_bits[stage] = bits;
     };
 
-    float m = -CUDART_INF_F, l = 0.f, o[8];
+    float m = -CUDART_INF_F, l = 0.f, o[C][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    for (int i = 0; i < C; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
         if (i < n_tiles) issue(i);
@@ -143,56 +166,70 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
         cp_commit();
         cp_wait<STAGES - 1>();
-        const int stage = i % STAGES;
-        const uint4* src = my_ring + stage * STAGE_U4;
-        unsigned bits = 0;
+        __syncwarp();                                   // other lanes' copies and zero fills are visible
+        const uint8_t* kt = my_ring + (i % STAGES) * 2 * TILE_BYTES;
+        const uint8_t* vt = kt + TILE_BYTES;
+        const int base = first_key + i * WARPS * TILE;
+        // scores of 16 keys against the query (row 0)
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        const int mi = lane >> 3;
 #pragma unroll
-        for (int st = 0; st < STAGES; ++st) bits = st == stage ? valid_bits[st] : bits;
-        float s[STEPS];
-        float tile_max = -CUDART_INF_F;
-#pragma unroll
-        for (int i2 = 0; i2 < STEPS; ++i2) {
-            float kf[8];
-            unpack8(src[i2 * 32 + lane], kf);
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc = fmaf(qv[j], kf[j], acc);
-#pragma unroll
-            for (int off = 1; off < C; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            s[i2] = ((bits >> i2) & 1u) ? acc : -CUDART_INF_F;
-            tile_max = fmaxf(tile_max, s[i2]);
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t b[4];
+            ldmatrix_x4(smem_addr(kt + tile_off<D>((mi >> 1) * 8 + (lane & 7), 2 * ks + (mi & 1))), b);
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
         }
+        // row 0 lives in lanes 0..3 (elements 0 and 1 of each 8-key tile); the other rows are idle
+        float mx = -CUDART_INF_F;
 #pragma unroll
-        for (int off = C; off < 32; off <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, off));
-        if (tile_max == -CUDART_INF_F) continue;
-        const float m_new = fmaxf(m, tile_max);
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = base + nt * 8 + 2 * t4 + e;
+                const float v = key < k1 ? s[nt][e] * scale_log2e : -CUDART_INF_F;
+                s[nt][e] = v;
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m, mx);               // every tile holds at least one live key
         const float corr = exp2f(m - m_new);
-        l *= corr;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] *= corr;
         m = m_new;
-#pragma unroll
-        for (int i2 = 0; i2 < STEPS; ++i2) {
-            const float p = exp2f(s[i2] - m_new);       // 0 for masked keys
-            l += p;
-            float vf[8];
-            unpack8(src[STEPS * 32 + i2 * 32 + lane], vf);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = fmaf(p, vf[j], o[j]);
+        l *= corr;
+        uint32_t pf[4];
+        {
+            const float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
+            const float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
+            l += (p00 + p01) + (p10 + p11);
+            pf[0] = g == 0 ? pack_bf16(p00, p01) : 0u;
+            pf[1] = 0u;
+            pf[2] = g == 0 ? pack_bf16(p10, p11) : 0u;
+            pf[3] = 0u;
         }
+#pragma unroll
+        for (int j = 0; j < C; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
+#pragma unroll
+        for (int dp = 0; dp < C / 2; ++dp) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(smem_addr(vt + tile_off<D>((mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1))), b);
+            mma_bf16(o[2 * dp], pf, b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+        }
+        __syncwarp();                                   // the stage may be refilled
     }
     cp_wait<0>();
-    // lanes with the same c hold different keys: add them up (l is the same in the C lanes of a key)
+    // row 0: lanes 0..3 hold dims 8j + 2*t4 + {0,1}; their sums of l differ by the keys each saw
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (g == 0) {
 #pragma unroll
-    for (int off = C; off < 32; off <<= 1) {
-        l += __shfl_xor_sync(0xffffffffu, l, off);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], off);
-    }
-    if (kg == 0) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sh_o[warp][c * 8 + j] = o[j];
-        if (c == 0) { sh_ml[warp][0] = m; sh_ml[warp][1] = l; }
+        for (int j = 0; j < C; ++j) {
+            sh_o[warp][j * 8 + 2 * t4] = o[j][0];
+            sh_o[warp][j * 8 + 2 * t4 + 1] = o[j][1];
+        }
+        if (t4 == 0) { sh_ml[warp][0] = m; sh_ml[warp][1] = l; }
     }
     __syncthreads();
     // combine the warps: thread d owns output dimension d
@@ -271,12 +308,13 @@ DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, c
     dim3 grid(n_splits, n_heads, n_tokens);
     const float scale_log2e = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
-    constexpr size_t RING = (size_t)WARPS * STAGES * 2 * STEPS * 32 * sizeof(uint4);
+    const size_t RING = (size_t)WARPS * STAGES * 2 * TILE * head_dim * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e1 = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RING);
-        cudaError_t e2 = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RING);
-        if (e1 != cudaSuccess || e2 != cudaSuccess) return dd_fail("dd_attention_decode: shared memory of %zu bytes refused", RING);
+        const int ring64 = WARPS * STAGES * 2 * TILE * 64 * 2, ring128 = WARPS * STAGES * 2 * TILE * 128 * 2;
+        cudaError_t e1 = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring64);
+        cudaError_t e2 = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring128);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) return dd_fail("dd_attention_decode: shared memory of %d bytes refused", ring128);
         configured = true;
     }
     if (head_dim == 64)
