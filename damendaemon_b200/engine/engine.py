@@ -87,6 +87,7 @@ class Engine:
         self.use_graph = use_graph and self.model.graph_safe
         self._graphs, self._seen = {}, set()
         self.max_graphs = 48                            # replayable step shapes kept; the least recently used goes first
+        self.max_graph_tokens = 4096                    # larger steps run eagerly (a graph keeps its activations)
         kernels.error_flag(self.device)                 # allocated before any graph capture
         if self.dtype == torch.bfloat16 and gemm != "simt":
             heads = max((getattr(l.mixer, "n_heads", 1) for l in self.spec.layers), default=1)
@@ -222,7 +223,7 @@ class Engine:
         decode_only = N == E
         slots, pos0 = self._upload(entries, lengths, at)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
-        if self.use_graph and M > 0:
+        if self.use_graph and M > 0 and N <= self.max_graph_tokens:
             # Every kernel reads lengths, positions and page tables from the metadata buffer, and launch shapes
             # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.
             key = (N, E, M, decode_only)

@@ -36,11 +36,52 @@ class WeightError(ValueError):
         self.wrong_shape, self.wrong_dtype, self.unequal = list(wrong_shape), list(wrong_dtype), list(unequal)
 
 
+def weight_files(model_dir) -> list:
+    """``model.safetensors``, or the shards that ``model.safetensors.index.json`` names (every shard the index
+    lists must exist; the reference cross-checks its index the same way, damendaemon/checkpoint.py:29-68)."""
+    folder = Path(model_dir)
+    single = folder / "model.safetensors"
+    if single.is_file():
+        return [single]
+    index = folder / "model.safetensors.index.json"
+    if index.is_file():
+        import json
+        try:
+            names = sorted(set(json.loads(index.read_text())["weight_map"].values()))
+        except (ValueError, KeyError, AttributeError, TypeError) as error:
+            raise WeightError(f"unreadable {index.name}: {error}") from error
+        shards = [folder / n for n in names]
+        gone = [p.name for p in shards if not p.is_file() or p.parent != folder]
+        if gone or not shards:
+            raise WeightError(f"{index.name} names shards that are not in {model_dir}: {gone}")
+        return shards
+    raise WeightError(f"no model.safetensors in {model_dir}")
+
+
 def weight_file(model_dir) -> Path:
-    path = Path(model_dir) / "model.safetensors"
-    if not path.is_file():
-        raise WeightError(f"no model.safetensors in {model_dir}")
-    return path
+    return weight_files(model_dir)[0]
+
+
+class ShardedSource:
+    """Several safetensors files read as one; a tensor name may appear in one shard only."""
+
+    def __init__(self, files):
+        self.files = files
+        self.where = {}
+        for f in files:
+            for name in f.names():
+                if name in self.where:
+                    raise WeightError(f"tensor {name} appears in two shards")
+                self.where[name] = f
+
+    def names(self):
+        return list(self.where)
+
+    def describe(self, name):
+        return self.where[name].describe(name)
+
+    def tensor(self, name):
+        return self.where[name].tensor(name)
 
 
 def check_and_place(source, spec, decls, engine_dtype, device):
@@ -123,5 +164,10 @@ class DictSource:
 
 
 def load_weights(model_dir, spec, decls, engine_dtype, device):
-    with SafetensorsFile(weight_file(model_dir)) as f:
-        return check_and_place(f, spec, decls, engine_dtype, device)
+    files = [SafetensorsFile(p) for p in weight_files(model_dir)]
+    try:
+        source = files[0] if len(files) == 1 else ShardedSource(files)
+        return check_and_place(source, spec, decls, engine_dtype, device)
+    finally:
+        for f in files:
+            f.close()

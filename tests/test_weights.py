@@ -106,3 +106,21 @@ def test_engine_refuses_without_cuda(tmp_path):
     folder = write_random_model(tmp_path / "m", TINY_A, 0)
     with pytest.raises(KernelError, match="no CPU fallback"):
         Engine(folder, dtype="float32")
+
+
+def test_sharded_checkpoint(tmp_path):
+    arch, typed, spec, decls = setup(TINY_A)
+    t = arch.random_tensors(typed, 0)
+    names = sorted(t)
+    half = len(names) // 2
+    write_safetensors(tmp_path / "model-00001-of-00002.safetensors", {n: t[n] for n in names[:half]})
+    write_safetensors(tmp_path / "model-00002-of-00002.safetensors", {n: t[n] for n in names[half:]})
+    index = {"weight_map": {n: ("model-00001-of-00002.safetensors" if i < half else "model-00002-of-00002.safetensors")
+                            for i, n in enumerate(names)}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    sharded = load_weights(tmp_path, spec, decls, torch.float32, "cpu")
+    whole = check_and_place(DictSource(t), spec, decls, torch.float32, "cpu")
+    assert all(torch.equal(sharded[k], whole[k]) for k in whole)
+    (tmp_path / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(WeightError, match="shards"):
+        load_weights(tmp_path, spec, decls, torch.float32, "cpu")
