@@ -73,9 +73,6 @@ __device__ __forceinline__ float activation_for(float u, int act, int out_dtype)
     return dd_activation(u, act);
 }
 
-// Epilogue of 16 consecutive tokens (m_first ..) of one output feature n. The residual may be
-// the output itself, so all 16 residual values are read before anything is written: the loads
-// stay independent instead of being ordered behind each store.
 // The cluster variant keeps a reduce buffer of (BM + 8) x BN floats beside the stages.
 template <int BN> struct ClusterConfig {
     // deep rings: with 5 stages (two blocks per SM, so that the next kernel's blocks could prefetch beside this
@@ -101,20 +98,63 @@ __device__ __forceinline__ void prefetch_share(const GemmParams& p) {
     }
 }
 
-__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc) {
-    const float b = p.bias ? p.bias[n] : 0.f;
-    float r[16];
+// Epilogue of 16 consecutive tokens (m_first ..) of one output feature n, specialised at compile time on the
+// activation, the output type and the presence of a residual, so that the element loop has no run-time choices
+// (with them in the loop the epilogue of a 128x128 tile took 14.6 us against 7.5 us, and it is the epilogue, not
+// the MMAs at 5 us, that bounds a K = 1600 tile). The residual may be the output itself, so all 16 residual
+// values are read before anything is written: the loads stay independent instead of being ordered behind each
+// store.
+template <int ACT, bool BF16_OUT, bool RESIDUAL>
+__device__ __forceinline__ void store16(const GemmParams& p, int m_first, int n, const float* acc, float b, const float* r) {
+    const int live = min(16, p.M - m_first);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (j >= live) break;
+        float v = acc[j] + b;
+        if (ACT == DD_ACT_GELU_NEW) {
+            if (BF16_OUT) {
+                float t;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                v = 0.5f * v * (1.0f + t);
+            } else v = dd_activation(v, DD_ACT_GELU_NEW);
+        } else if (ACT == DD_ACT_GELU_ERF) v = dd_activation(v, DD_ACT_GELU_ERF);
+        if (RESIDUAL) v += r[j];
+        if (BF16_OUT) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)(m_first + j) * p.ldo + n] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(p.out)[(size_t)(m_first + j) * p.ldo + n] = v;
+    }
+}
+
+template <int ACT, bool BF16_OUT>
+__device__ __forceinline__ void store16_r(const GemmParams& p, int m_first, int n, const float* acc, float b, const float* r) {
+    if (p.residual) store16<ACT, BF16_OUT, true>(p, m_first, n, acc, b, r);
+    else store16<ACT, BF16_OUT, false>(p, m_first, n, acc, b, r);
+}
+
+template <int ACT>
+__device__ __forceinline__ void store16_o(const GemmParams& p, int m_first, int n, const float* acc, float b, const float* r) {
+    if (p.out_dtype == DD_BF16) store16_r<ACT, true>(p, m_first, n, acc, b, r);
+    else store16_r<ACT, false>(p, m_first, n, acc, b, r);
+}
+
+// The 16 residual values of tokens m_first.. at feature n (zeros without a residual or past the last token).
+__device__ __forceinline__ void load_residual16(const GemmParams& p, int m_first, int n, float* r) {
 #pragma unroll
     for (int j = 0; j < 16; ++j)
         r[j] = (p.residual && m_first + j < p.M) ? p.residual[(size_t)(m_first + j) * p.ldr + n] : 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int m = m_first + j;
-        if (m >= p.M) break;
-        const float v = activation_for(acc[j] + b, p.act, p.out_dtype) + r[j];
-        if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-        else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-    }
+}
+
+// r: residual values already loaded (load_residual16), issued by the caller before it waits for the accumulator.
+__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc, const float* r) {
+    const float b = p.bias ? p.bias[n] : 0.f;
+    if (p.act == DD_ACT_NONE) store16_o<DD_ACT_NONE>(p, m_first, n, acc, b, r);
+    else if (p.act == DD_ACT_GELU_NEW) store16_o<DD_ACT_GELU_NEW>(p, m_first, n, acc, b, r);
+    else store16_o<DD_ACT_GELU_ERF>(p, m_first, n, acc, b, r);
+}
+
+__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc) {
+    float r[16];
+    load_residual16(p, m_first, n, r);
+    store_out16(p, m_first, n, acc, r);
 }
 
 template <int BN>
@@ -225,6 +265,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 // the epilogue must have drained this accumulator (passes at once the first two times)
                 if (!tc::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1) ^ 1, abort_flag)) break;
                 tc::fence_after_sync();
+                if (p.timeline && local < 3) p.timeline[blockIdx.x * 16 + 1 + 4 * local] = tc::global_ns();
                 const uint32_t tmem_d = tmem_base + acc * C::ACC_COLS;
                 for (int i = 0; i < n_kblocks; ++i, ++it) {
                     const int s = it % C::STAGES;
@@ -241,11 +282,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                     tc::mma_commit(&empty_bar[s]);     // the stage is free once these MMAs have read it
                 }
+                if (p.timeline && local < 3) p.timeline[blockIdx.x * 16 + 2 + 4 * local] = tc::global_ns();
                 if (ok) tc::mma_commit(&tmem_full_bar[acc]);   // the accumulator is complete
             }
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. 32*(w%4)+31
+        if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 16] = tc::global_ns();
         dd_grid_wait();              // bias is constant, but residual, workspace and counters are earlier kernels' data
         const int quarter = warp & 3;
         uint32_t local = 0;
@@ -259,11 +302,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (*epilogue_abort) break;                   // the same decision in all four warps
             tc::fence_after_sync();
+            if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 3 + 4 * local] = tc::global_ns();
             const uint32_t lane_addr = tmem_base + acc * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             if (p.splits == 1) {
                 for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
+                    float res[16];
+                    if (n_ok) load_residual16(p, m0 + c0, n, res);       // in flight while the accumulator is read
                     tc::tmem_ld_wait();
                     if (c0 + 16 >= BN || m0 + c0 + 16 >= p.M) {      // last read of this accumulator: hand it back
                         tc::fence_before_sync();
@@ -274,9 +320,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         float accv[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
-                        store_out16(p, m0 + c0, n, accv);
+                        store_out16(p, m0 + c0, n, accv, res);
                     }
                 }
+                if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 4 + 4 * local] = tc::global_ns();
             } else {
                 // partial sums to the workspace, then the last CTA of this tile reduces
                 float* ws = p.workspace + (size_t)split * p.M * p.N;
@@ -345,6 +392,167 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Two SMs on one tile (tcgen05 cta_group::2), for steps of many tokens: a cluster of two blocks owns 256 output
+// features x BN tokens. Each block loads its own 128 weight rows and its own half of the token rows with TMA, all
+// bytes counted on the leader's barrier; the leader (rank 0) issues tcgen05.mma.cta_group::2, which reads both
+// blocks' shared memory and leaves each block its 128 x BN half of the accumulator in its own TMEM; tcgen05.commit
+// with a cluster mask frees the stages and publishes the accumulator in both blocks. Per block and k-block this
+// moves 16 KB + BN/2 x 128 B for a 128 x BN x 64 product: half the L2-to-SM traffic per flop of the one-SM tile.
+template <int BN> struct PairConfig {
+    static constexpr int HALF = BN / 2;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = HALF * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN >= 256 ? 6 : (BN >= 192 ? 7 : 8);
+    static constexpr int ACC_COLS = BN == 192 ? 256 : BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                         const GemmParams p) {
+    using C = PairConfig<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);   // used in the leader only
+    uint64_t* empty_bar = full_bar + C::STAGES;
+    uint64_t* tmem_full_bar = empty_bar + C::STAGES;      // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;         // [2] used in the leader only: 8 epilogue warps arrive
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* epilogue_abort = const_cast<int*>(abort_flag) + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_n = (p.N + 2 * BM - 1) / (2 * BM);
+    const int tiles_m = (p.M + BN - 1) / BN;
+    const int n_items = tiles_n * tiles_m;
+    const int n_kblocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            tc::mbar_init(&tmem_full_bar[a], 1);
+            tc::mbar_init(&tmem_empty_bar[a], 8);
+        }
+        *abort_flag = 0;
+        *epilogue_abort = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+        tc::tmem_relinquish_pair();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_arrive();
+    tc::cluster_wait();                  // the other block's barriers exist before anything signals them
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    dd_launch_dependents();
+
+#define DD_PAIR_COORDS(item)                                     \
+    const int n0 = ((item) % tiles_n) * 2 * BM + (int)rank * BM; \
+    const int m0 = ((item) / tiles_n) * BN;
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::prefetch_tensormap(&map_w);
+            tc::prefetch_tensormap(&map_x);
+            dd_grid_wait();
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = pair; item < n_items && ok; item += n_pairs) {
+                DD_PAIR_COORDS(item)
+                for (int i = 0; i < n_kblocks; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    if (!tc::mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + C::A_BYTES;
+                    if (rank == 0) tc::mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);     // both blocks' bytes
+                    const uint32_t leader_full = tc::map_to_rank(&full_bar[s], 0);
+                    tc::tma_load_2d_pair(a_dst, &map_w, i * BK, n0, leader_full);
+                    tc::tma_load_2d_pair(b_dst, &map_x, i * BK, m0 + (int)rank * C::HALF, leader_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && tc::elect_one()) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(2 * BM, BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int item = pair; item < n_items && ok; item += n_pairs, ++local) {
+                const uint32_t acc = local & 1;
+                if (!tc::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1) ^ 1, abort_flag)) break;
+                tc::fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc * C::ACC_COLS;
+                for (int i = 0; i < n_kblocks; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    if (!tc::mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag)) { ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t a_addr = tc::smem_u32(tiles + s * C::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc::mma_bf16_pair(tmem_d, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2),
+                                          tc::smem_desc_sw128(b_addr + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc::mma_commit_pair(&empty_bar[s], 3);            // the stage is free in both blocks
+                }
+                if (ok) tc::mma_commit_pair(&tmem_full_bar[acc], 3);   // both halves of the accumulator are complete
+            }
+        }
+    } else {
+        dd_grid_wait();
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        for (int item = pair; item < n_items; item += n_pairs, ++local) {
+            DD_PAIR_COORDS(item)
+            const uint32_t acc = local & 1;
+            const int n = n0 + quarter * 32 + lane;
+            const bool n_ok = n < p.N;
+            if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*epilogue_abort) break;
+            tc::fence_after_sync();
+            const uint32_t lane_addr = tmem_base + acc * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                uint32_t r[16];
+                tc::tmem_ld_x16(lane_addr + c0, r);
+                tc::tmem_ld_wait();
+                if (c0 + 16 >= BN || m0 + c0 + 16 >= p.M) {           // last read: hand the accumulator back to the leader
+                    tc::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
+                }
+                if (n_ok) {
+                    float accv[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
+                    store_out16(p, m0 + c0, n, accv);
+                }
+            }
+        }
+    }
+#undef DD_PAIR_COORDS
+    __syncwarp();
+    tc::fence_before_sync();
+    tc::cluster_arrive();
+    tc::cluster_wait();                  // neither block leaves while the other may still read its tiles or signal its barriers
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 8);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
 }
 
@@ -598,9 +806,48 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParam
     return dd_check_launch("dd_gemm_tcgen05");
 }
 
+template <int BN>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t s) {
+    using C = PairConfig<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const int items = dd_ceil_div(p.N, 2 * BM) * dd_ceil_div(p.M, BN);
+    const int pairs = items < sm_count / 2 ? items : sm_count / 2;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * pairs);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = s;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attrs;
+    config.numAttrs = dd_pdl_enabled ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_pair_kernel<BN>, mw, mx, p);
+    if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05 (two SMs per tile): %s", cudaGetErrorString(e));
+    return dd_check_launch("dd_gemm_tcgen05");
+}
+
 }  // namespace
 
-// Debugging aid: a device buffer of 8 * blocks time stamps that the cluster kernel fills (null switches it off).
+// Debugging aid: a device buffer of time stamps (ns) that the kernels fill, null switches it off: 8 per block from
+// the cluster kernel; 16 per block from the persistent kernel (0 start, then for the first three tiles: MMAs begin,
+// MMAs issued, epilogue begins, epilogue done).
 DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
 
 // Chooses the token tile, the K split and how the split is reduced (*cluster = 1: inside a thread-block
@@ -611,14 +858,21 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     int bn = 128;
     if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64;
     else {
+        // Wide outputs (measured at 4800 and 6400 features: 5-10% faster) go to two SMs per 256-feature tile;
+        // with 1600 features the 256-feature tiles waste an eighth of their rows and the one-SM kernel wins.
+        const bool pair = N >= 2048 && cluster != nullptr;
+        const int rows = pair ? 2 * BM : BM, units = pair ? sm_count / 2 : sm_count;
         long long best = -1;
         const int candidates[3] = {128, 192, 256};
         for (int i = 0; i < 3; ++i) {
             const int c = candidates[i];
-            const long long t = (long long)dd_ceil_div(N, BM) * dd_ceil_div(M, c);
-            const long long cost = (long long)dd_ceil_div(t, sm_count) * c;
+            const long long t = (long long)dd_ceil_div(N, rows) * dd_ceil_div(M, c);
+            const long long cost = (long long)dd_ceil_div(t, units) * c;
             if (best < 0 || cost < best) { best = cost; bn = c; }
         }
+        if (token_tile) *token_tile = bn;
+        if (cluster) *cluster = pair ? 2 : 0;
+        return 1;
     }
     if (token_tile) *token_tile = bn;
     if (cluster) *cluster = 0;
@@ -642,6 +896,7 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
 // X [M,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw); bias [N] f32 or null; residual [M,N] f32
 // (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). cluster = 1: splits
 // (at most 8) are the blocks of a cluster and reduce over distributed shared memory (token_tile <= 64);
+// cluster = 2: two SMs per 256-feature tile (tcgen05 cta_group::2), token_tile 128/192/256, no split;
 // cluster = 0 with splits > 1: workspace f32 [splits*M*N] and counters int32 [tiles], zero before the
 // first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
 // weight matrix of a decode step): this kernel's blocks ask L2 to fetch it while they run.
@@ -656,8 +911,10 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     if (out_dtype != DD_BF16 && out_dtype != DD_F32) return dd_fail("dd_gemm_tcgen05: unknown output dtype %d", out_dtype);
     const int kblocks = dd_ceil_div(K, BK);
     if (splits < 1 || splits > kblocks) return dd_fail("dd_gemm_tcgen05: bad split count %d for %d k-blocks", splits, kblocks);
-    if (cluster && (splits > 8 || token_tile > 64))
+    if (cluster == 1 && (splits > 8 || token_tile > 64))
         return dd_fail("dd_gemm_tcgen05: a cluster has at most 8 blocks and a token tile of at most 64 (got %d, %d)", splits, token_tile);
+    if (cluster == 2 && (splits != 1 || (token_tile != 128 && token_tile != 192 && token_tile != 256)))
+        return dd_fail("dd_gemm_tcgen05: two SMs per tile take no K split and a token tile of 128, 192 or 256 (got %d, %d)", splits, token_tile);
     GemmParams p;
     p.bias = bias; p.residual = residual; p.out = out; p.workspace = workspace; p.counters = counters;
     p.error_flag = error_flag; p.M = M; p.N = N; p.K = K; p.ldr = ldr; p.ldo = ldo; p.act = act; p.out_dtype = out_dtype;
@@ -666,7 +923,7 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     p.prefetch_bytes = (prefetch && prefetch_bytes > 0 && !((uintptr_t)prefetch & 15)) ? (unsigned long long)prefetch_bytes : 0;
     p.splits = splits; p.kblocks_per_split = dd_ceil_div(kblocks, splits);
     p.splits = dd_ceil_div(kblocks, p.kblocks_per_split);     // no empty split
-    if (p.splits == 1) cluster = 0;
+    if (p.splits == 1 && cluster == 1) cluster = 0;
     if (p.splits > 1 && !cluster) {
         const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, token_tile);
         if (!workspace || !counters || n_counters < tiles)
@@ -674,8 +931,15 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     }
     CUtensorMap mw, mx;
     if (int e = make_map(&mw, W, N, K, ldw, BM, "the weight matrix")) return e;
-    if (int e = make_map(&mx, X, M, K, ldx, token_tile, "the activations")) return e;
+    if (int e = make_map(&mx, X, M, K, ldx, cluster == 2 ? token_tile / 2 : token_tile, "the activations")) return e;
     cudaStream_t s = (cudaStream_t)stream;
+    if (cluster == 2) {
+        switch (token_tile) {
+            case 128: return launch_pair<128>(mw, mx, p, s);
+            case 192: return launch_pair<192>(mw, mx, p, s);
+            case 256: return launch_pair<256>(mw, mx, p, s);
+        }
+    }
     if (cluster) {
         switch (token_tile) {
             case 16: return launch_cluster<16>(mw, mx, p, s);

@@ -88,6 +88,26 @@ def test_cluster_split(K, splits, tokens, tile):
     assert (gelu.double() - want).abs().max() < 2.0 ** -8 * float(want.abs().max()) + 1e-3
 
 
+@pytest.mark.parametrize("tile", [128, 192, 256])
+@pytest.mark.parametrize("shape", [(300, 257, 1608), (2048, 1600, 1600), (1000, 4800, 320), (130, 515, 64)])
+def test_two_sms_per_tile(K, tile, shape):
+    """tcgen05 cta_group::2: a cluster of two blocks on one 256-feature tile, every epilogue."""
+    M, N, Kd = shape
+    a, w, bias, res = operands(M, N, Kd, seed=6)
+    ref = a.double() @ w.double().t() + bias.double()
+    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=1, token_tile=tile, cluster=2)
+    assert K.read_error_flag(DEV) == 0
+    assert (out.double() - ref).abs().max() < 5e-4 * math.sqrt(Kd / 64)
+    assert torch.equal(out, K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=1, token_tile=128, cluster=0))
+    stream = res.clone()
+    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream, splits=1, token_tile=tile, cluster=2)
+    assert (stream.double() - (ref + res.double())).abs().max() < 5e-4 * math.sqrt(Kd / 64)
+    half = K.gemm_tcgen05(a, w, bias, activation="gelu_new", splits=1, token_tile=tile, cluster=2)
+    want = 0.5 * ref * (1 + torch.tanh(math.sqrt(2 / math.pi) * (ref + 0.044715 * ref ** 3)))
+    assert (half.double() - want).abs().max() < 2.0 ** -7 * float(want.abs().max()) + 1e-3
+    assert K.read_error_flag(DEV) == 0
+
+
 def test_strided_views_and_refusals(K):
     a, w, bias, res = operands(20, 256, 128, seed=3)
     wide = torch.zeros(20, 128 + 64, dtype=torch.bfloat16, device=DEV)
