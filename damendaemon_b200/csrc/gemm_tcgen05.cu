@@ -31,7 +31,9 @@ namespace {
 constexpr int BM = 128;          // output features per tile (tcgen05.mma M)
 constexpr int BK = 64;           // k elements per stage: one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;     // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int THREADS = 192;     // cluster kernel: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int EPI_WARPS = 8;     // persistent and two-SM kernels: two warps per TMEM lane quarter, each half of the tokens
+constexpr int THREADS_P = 64 + 32 * EPI_WARPS;
 
 struct GemmParams {
     const float* bias;           // [N] or null
@@ -44,6 +46,7 @@ struct GemmParams {
     int ldr, ldo;
     int act, out_dtype;
     int splits, kblocks_per_split;
+    int vec;                     // out, residual and bias allow 16-byte accesses at every row start (tiles of 128 tokens)
     const uint8_t* prefetch;        // null, or memory a later kernel will stream (the next weight matrix):
     unsigned long long prefetch_bytes;   // every block asks L2 to fetch its share while this kernel runs
     unsigned long long* timeline;   // null, or 8 time stamps (ns) per block for looking at where a block's time goes
@@ -52,6 +55,7 @@ struct GemmParams {
 unsigned long long* g_timeline = nullptr;
 
 template <int BN> struct Config {
+    static constexpr bool BY_TOKEN = BN >= 128;      // accumulator lanes are tokens (else output features)
     static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 192 ? 4 : (BN >= 128 ? 6 : 8));
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
@@ -157,11 +161,118 @@ __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, in
     store_out16(p, m_first, n, acc, r);
 }
 
+// ---- epilogue of tiles whose accumulator lanes are tokens (tiles of 128 tokens x BN features) ----
+// A thread holds 16 consecutive features n_first.. of its own token m: the bias comes in four 16-byte loads
+// that are the same for every thread, the residual and the result move as 16-byte pieces of the thread's own row.
+// With one output feature per thread instead (the orientation of the few-token tiles) a 128 x 128 tile needs 16
+// scalar stores per thread and chunk, and that epilogue, not the MMAs, bounded the tiles of a 2,048-token step.
+__device__ __forceinline__ void load_residual_row16(const GemmParams& p, int m, int n_first, float* r) {
+    if (!p.residual) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0.f;
+        return;
+    }
+    const float* src = p.residual + (size_t)m * p.ldr + n_first;
+    if (p.vec && n_first + 16 <= p.N) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 v = *reinterpret_cast<const float4*>(src + 4 * q);
+            r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = n_first + j < p.N ? src[j] : 0.f;
+    }
+}
+
+template <int ACT, bool BF16_OUT, bool RESIDUAL>
+__device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
+    const bool whole = p.vec && n_first + 16 <= p.N;
+    float v[16];
+    if (p.bias && whole) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + n_first) + q);
+            v[4 * q] = b.x; v[4 * q + 1] = b.y; v[4 * q + 2] = b.z; v[4 * q + 3] = b.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = (p.bias && n_first + j < p.N) ? __ldg(p.bias + n_first + j) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float u = __uint_as_float(acc[j]) + v[j];
+        if (ACT == DD_ACT_GELU_NEW) {
+            if (BF16_OUT) {
+                float t;
+                asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+                u = 0.5f * u * (1.0f + t);
+            } else u = dd_activation(u, DD_ACT_GELU_NEW);
+        } else if (ACT == DD_ACT_GELU_ERF) u = dd_activation(u, DD_ACT_GELU_ERF);
+        if (RESIDUAL) u += r[j];
+        v[j] = u;
+    }
+    if (BF16_OUT) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + n_first;
+        if (whole) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * i], v[8 * q + 2 * i + 1]);
+                    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (n_first + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+    } else {
+        float* dst = reinterpret_cast<float*>(p.out) + (size_t)m * p.ldo + n_first;
+        if (whole) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (n_first + j < p.N) dst[j] = v[j];
+        }
+    }
+}
+
+template <int ACT, bool BF16_OUT>
+__device__ __forceinline__ void store_row16_r(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
+    if (p.residual) store_row16<ACT, BF16_OUT, true>(p, m, n_first, acc, r);
+    else store_row16<ACT, BF16_OUT, false>(p, m, n_first, acc, r);
+}
+
+template <int ACT>
+__device__ __forceinline__ void store_row16_o(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
+    if (p.out_dtype == DD_BF16) store_row16_r<ACT, true>(p, m, n_first, acc, r);
+    else store_row16_r<ACT, false>(p, m, n_first, acc, r);
+}
+
+__device__ __forceinline__ void store_out_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
+    if (p.act == DD_ACT_NONE) store_row16_o<DD_ACT_NONE>(p, m, n_first, acc, r);
+    else if (p.act == DD_ACT_GELU_NEW) store_row16_o<DD_ACT_GELU_NEW>(p, m, n_first, acc, r);
+    else store_row16_o<DD_ACT_GELU_ERF>(p, m, n_first, acc, r);
+}
+
+// One SM per tile, persistent over tiles, two accumulators in TMEM so that the epilogue of one tile runs under the
+// MMAs of the next. The 128 accumulator lanes (operand A, map_a) are output features when BN <= 64, the
+// orientation for a few tokens: the weights fill the 128-row side of the MMA whatever the token count, and a
+// thread of the epilogue owns one feature. For BN >= 128 the lanes are tokens and the BN columns are features,
+// so that a thread of the epilogue owns a piece of one output row and moves it in 16-byte accesses.
 template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+__global__ void __launch_bounds__(THREADS_P, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
     using C = Config<BN>;
+    constexpr bool BY_TOKEN = C::BY_TOKEN;
     extern __shared__ uint8_t smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -175,10 +286,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     int* epilogue_abort = last_flag + 1;                  // written by epilogue threads only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = (p.N + BM - 1) / BM;              // tiles along the output features
-    const int tiles_m = (p.M + BN - 1) / BN;              // tiles along the tokens
-    const int n_items = tiles_n * tiles_m * p.splits;
+    const int rows_a = BY_TOKEN ? p.M : p.N, rows_b = BY_TOKEN ? p.N : p.M;
+    const int tiles_a = (rows_a + BM - 1) / BM;
+    const int tiles_b = (rows_b + BN - 1) / BN;
+    const int n_items = tiles_a * tiles_b * p.splits;
     const int total_kblocks = (p.K + BK - 1) / BK;
+    // which operand holds the weights
+    const CUtensorMap* map_w = BY_TOKEN ? &map_b : &map_a;
+    const CUtensorMap* map_x = BY_TOKEN ? &map_a : &map_b;
+    constexpr int W_OFFSET = BY_TOKEN ? C::A_BYTES : 0, X_OFFSET = BY_TOKEN ? 0 : C::A_BYTES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -187,7 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             tc::mbar_init(&tmem_full_bar[a], 1);
-            tc::mbar_init(&tmem_empty_bar[a], 4);         // one arrival per epilogue warp
+            tc::mbar_init(&tmem_empty_bar[a], EPI_WARPS);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         *last_flag = 0;
@@ -205,20 +321,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     dd_launch_dependents();      // the next kernel may begin its own set-up now
 
-    // Work item -> (feature tile, token tile, split). Feature tiles vary fastest, so CTAs that run
-    // side by side share the same token tile in L2.
+    // Work item -> (tile along A, tile along B, split). Tiles along A vary fastest, so blocks that run side by
+    // side share the same B tile in L2.
 #define DD_ITEM_COORDS(item)                                              \
     const int split = (item) % p.splits;                                  \
     const int tile = (item) / p.splits;                                   \
-    const int n0 = (tile % tiles_n) * BM;                                 \
-    const int m0 = (tile / tiles_n) * BN;                                 \
+    const int a0 = (tile % tiles_a) * BM;                                 \
+    const int b0 = (tile / tiles_a) * BN;                                 \
+    const int w0 = BY_TOKEN ? b0 : a0, x0 = BY_TOKEN ? a0 : b0;           \
     const int kb_begin = split * p.kblocks_per_split;                     \
     const int n_kblocks = min(total_kblocks, kb_begin + p.kblocks_per_split) - kb_begin;
 
     if (warp == 0) {
         if (tc::elect_one()) {
-            tc::prefetch_tensormap(&map_w);
-            tc::prefetch_tensormap(&map_x);
+            tc::prefetch_tensormap(&map_a);
+            tc::prefetch_tensormap(&map_b);
             uint32_t it = 0;                               // k-blocks issued so far, across items
             bool ok = true;
             // Weights never change, so the weight tiles of the first stages are requested before the
@@ -226,11 +343,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             int ahead = 0;
             if (blockIdx.x < n_items) {
                 DD_ITEM_COORDS(blockIdx.x)
-                (void)m0;
+                (void)x0;
                 ahead = min(n_kblocks, C::STAGES);
                 for (int i = 0; i < ahead; ++i) {
                     tc::mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
-                    tc::tma_load_2d(tiles + i * C::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+                    tc::tma_load_2d(tiles + i * C::STAGE_BYTES + W_OFFSET, map_w, (kb_begin + i) * BK, w0, &full_bar[i]);
                 }
             }
             prefetch_share(p);
@@ -239,17 +356,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 DD_ITEM_COORDS(item)
                 for (int i = 0; i < n_kblocks; ++i, ++it) {
                     const int s = it % C::STAGES;
-                    uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
-                    uint8_t* b_dst = a_dst + C::A_BYTES;
+                    uint8_t* stage = tiles + s * C::STAGE_BYTES;
                     if ((int)it < ahead) {                 // the weight tile of this stage is already on its way
-                        tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+                        tc::tma_load_2d(stage + X_OFFSET, map_x, (kb_begin + i) * BK, x0, &full_bar[s]);
                         continue;
                     }
                     const uint32_t phase = (it / C::STAGES) & 1;
                     if (!tc::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     tc::mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-                    tc::tma_load_2d(a_dst, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
-                    tc::tma_load_2d(b_dst, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+                    tc::tma_load_2d(stage + W_OFFSET, map_w, (kb_begin + i) * BK, w0, &full_bar[s]);
+                    tc::tma_load_2d(stage + X_OFFSET, map_x, (kb_begin + i) * BK, x0, &full_bar[s]);
                 }
             }
         }
@@ -260,7 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bool ok = true;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local) {
                 DD_ITEM_COORDS(item)
-                (void)n0; (void)m0;
+                (void)w0; (void)x0;
                 const uint32_t acc = local & 1;
                 // the epilogue must have drained this accumulator (passes at once the first two times)
                 if (!tc::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1) ^ 1, abort_flag)) break;
@@ -291,52 +407,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 16] = tc::global_ns();
         dd_grid_wait();              // bias is constant, but residual, workspace and counters are earlier kernels' data
         const int quarter = warp & 3;
+        // the two warps of a lane quarter split the tile's columns in halves (in chunks of 16)
+        constexpr int FIRST_HALF = ((BN / 16 + 1) / 2) * 16;
+        const int c_begin = warp >= 6 ? FIRST_HALF : 0;
+        const int c_limit = warp >= 6 ? BN : FIRST_HALF;
         uint32_t local = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++local) {
             DD_ITEM_COORDS(item)
-            (void)n_kblocks;
+            (void)n_kblocks; (void)w0; (void)x0;
             const uint32_t acc = local & 1;
-            const int n = n0 + quarter * 32 + lane;
-            const bool n_ok = n < p.N;
+            const int row = a0 + quarter * 32 + lane;      // this thread's token (BY_TOKEN) or output feature
+            const bool row_ok = row < rows_a;
             if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*epilogue_abort) break;                   // the same decision in all four warps
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*epilogue_abort) break;                   // the same decision in all eight warps
             tc::fence_after_sync();
             if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 3 + 4 * local] = tc::global_ns();
             const uint32_t lane_addr = tmem_base + acc * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            if (c_begin >= c_limit || b0 + c_begin >= rows_b) {      // no columns for this warp in this tile
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
+            }
             if (p.splits == 1) {
-                for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                for (int c0 = c_begin; c0 < c_limit && b0 + c0 < rows_b; c0 += 16) {
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
                     float res[16];
-                    if (n_ok) load_residual16(p, m0 + c0, n, res);       // in flight while the accumulator is read
+                    if (row_ok) {                                        // in flight while the accumulator is read
+                        if (BY_TOKEN) load_residual_row16(p, row, b0 + c0, res);
+                        else load_residual16(p, b0 + c0, row, res);
+                    }
                     tc::tmem_ld_wait();
-                    if (c0 + 16 >= BN || m0 + c0 + 16 >= p.M) {      // last read of this accumulator: hand it back
+                    if (c0 + 16 >= c_limit || b0 + c0 + 16 >= rows_b) {  // this warp's last read of the accumulator
                         tc::fence_before_sync();
                         __syncwarp();
                         if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
                     }
-                    if (n_ok) {
-                        float accv[16];
+                    if (row_ok) {
+                        if (BY_TOKEN) store_out_row16(p, row, b0 + c0, r, res);
+                        else {
+                            float accv[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
-                        store_out16(p, m0 + c0, n, accv, res);
+                            for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
+                            store_out16(p, b0 + c0, row, accv, res);
+                        }
                     }
                 }
                 if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 4 + 4 * local] = tc::global_ns();
-            } else {
-                // partial sums to the workspace, then the last CTA of this tile reduces
+            } else if (!BY_TOKEN) {
+                // partial sums to the workspace, then the last block of this tile reduces
+                const int n = row, m0 = b0;
                 float* ws = p.workspace + (size_t)split * p.M * p.N;
-                for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                for (int c0 = c_begin; c0 < c_limit && m0 + c0 < p.M; c0 += 16) {
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
                     tc::tmem_ld_wait();
-                    if (c0 + 16 >= BN || m0 + c0 + 16 >= p.M) {
+                    if (c0 + 16 >= c_limit || m0 + c0 + 16 >= p.M) {
                         tc::fence_before_sync();
                         __syncwarp();
                         if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
                     }
-                    if (n_ok) {
+                    if (row_ok) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int m = m0 + c0 + j;
@@ -345,41 +477,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     const int prev = atomicAdd(&p.counters[tile], 1);
                     *last_flag = (prev == p.splits - 1) ? 1 : 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 const bool last = *last_flag != 0;
                 if (last) {
                     __threadfence();
-                    if (n_ok) {
-                        // 16 tokens at a time, so that 16 independent loads are in flight for every split
-                        for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+                    if (row_ok) {
+                        // 16 tokens at a time, so that 16 independent loads are in flight; splits are added in
+                        // ascending order (deterministic)
+                        for (int c0 = c_begin; c0 < c_limit && m0 + c0 < p.M; c0 += 16) {
                             float v[16];
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                            // splits are added in ascending order (deterministic), two splits' loads in flight at once
-                            for (int s0 = 0; s0 < p.splits; s0 += 2) {
-                                float t[2][16];
+                            for (int s0 = 0; s0 < p.splits; ++s0) {
+                                const float* src = p.workspace + ((size_t)s0 * p.M + m0 + c0) * p.N + n;
+                                float t[16];
 #pragma unroll
-                                for (int u = 0; u < 2; ++u) {
-                                    const float* src = p.workspace + ((size_t)(s0 + u) * p.M + m0 + c0) * p.N + n;
+                                for (int j = 0; j < 16; ++j) t[j] = m0 + c0 + j < p.M ? __ldcg(src + (size_t)j * p.N) : 0.f;
 #pragma unroll
-                                    for (int j = 0; j < 16; ++j)
-                                        t[u][j] = (s0 + u < p.splits && m0 + c0 + j < p.M) ? __ldcg(src + (size_t)j * p.N) : 0.f;
-                                }
-#pragma unroll
-                                for (int u = 0; u < 2; ++u)
-#pragma unroll
-                                    for (int j = 0; j < 16; ++j) v[j] += t[u][j];
+                                for (int j = 0; j < 16; ++j) v[j] += t[j];
                             }
                             store_out16(p, m0 + c0, n, v);
                         }
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");        // last_flag is reused by the next item
+                asm volatile("bar.sync 1, 256;" ::: "memory");        // last_flag is reused by the next item
                 if (last && warp == 2 && lane == 0) p.counters[tile] = 0;
             }
         }
@@ -395,12 +521,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
-// Two SMs on one tile (tcgen05 cta_group::2), for steps of many tokens: a cluster of two blocks owns 256 output
-// features x BN tokens. Each block loads its own 128 weight rows and its own half of the token rows with TMA, all
-// bytes counted on the leader's barrier; the leader (rank 0) issues tcgen05.mma.cta_group::2, which reads both
-// blocks' shared memory and leaves each block its 128 x BN half of the accumulator in its own TMEM; tcgen05.commit
-// with a cluster mask frees the stages and publishes the accumulator in both blocks. Per block and k-block this
-// moves 16 KB + BN/2 x 128 B for a 128 x BN x 64 product: half the L2-to-SM traffic per flop of the one-SM tile.
+// Two SMs on one tile (tcgen05 cta_group::2), for steps of many tokens: a cluster of two blocks owns 256 tokens
+// x BN output features. Each block loads its own 128 token rows and its own half of the BN weight rows with TMA,
+// all bytes counted on the leader's barrier; the leader (rank 0) issues tcgen05.mma.cta_group::2, which reads both
+// blocks' shared memory and leaves each block the 128 x BN accumulator of its own tokens in its own TMEM;
+// tcgen05.commit with a cluster mask frees the stages and publishes the accumulator in both blocks. Per block and
+// k-block this moves 16 KB + BN/2 x 128 B for a 128 x BN x 64 product: less L2-to-SM traffic per flop than the
+// one-SM tile, which at 2,048 tokens is what bounds it.
 template <int BN> struct PairConfig {
     static constexpr int HALF = BN / 2;
     static constexpr int A_BYTES = BM * BK * 2;
@@ -413,7 +540,7 @@ template <int BN> struct PairConfig {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS_P, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                          const GemmParams p) {
     using C = PairConfig<BN>;
@@ -430,9 +557,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_rank();
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int tiles_n = (p.N + 2 * BM - 1) / (2 * BM);
-    const int tiles_m = (p.M + BN - 1) / BN;
-    const int n_items = tiles_n * tiles_m;
+    const int tiles_a = (p.M + 2 * BM - 1) / (2 * BM);     // along the tokens, 256 per pair
+    const int tiles_b = (p.N + BN - 1) / BN;               // along the output features
+    const int n_items = tiles_a * tiles_b;
     const int n_kblocks = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -442,7 +569,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         }
         for (int a = 0; a < 2; ++a) {
             tc::mbar_init(&tmem_full_bar[a], 1);
-            tc::mbar_init(&tmem_empty_bar[a], 8);
+            tc::mbar_init(&tmem_empty_bar[a], 2 * EPI_WARPS);
         }
         *abort_flag = 0;
         *epilogue_abort = 0;
@@ -462,8 +589,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     dd_launch_dependents();
 
 #define DD_PAIR_COORDS(item)                                     \
-    const int n0 = ((item) % tiles_n) * 2 * BM + (int)rank * BM; \
-    const int m0 = ((item) / tiles_n) * BN;
+    const int a0 = ((item) % tiles_a) * 2 * BM + (int)rank * BM; \
+    const int b0 = ((item) / tiles_a) * BN;
 
     if (warp == 0) {
         if (tc::elect_one()) {
@@ -481,8 +608,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     uint8_t* b_dst = a_dst + C::A_BYTES;
                     if (rank == 0) tc::mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);     // both blocks' bytes
                     const uint32_t leader_full = tc::map_to_rank(&full_bar[s], 0);
-                    tc::tma_load_2d_pair(a_dst, &map_w, i * BK, n0, leader_full);
-                    tc::tma_load_2d_pair(b_dst, &map_x, i * BK, m0 + (int)rank * C::HALF, leader_full);
+                    tc::tma_load_2d_pair(a_dst, &map_x, i * BK, a0, leader_full);
+                    tc::tma_load_2d_pair(b_dst, &map_w, i * BK, b0 + (int)rank * C::HALF, leader_full);
                 }
             }
         }
@@ -514,32 +641,38 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     } else {
         dd_grid_wait();
         const int quarter = warp & 3;
+        // the two warps of a lane quarter split the tile's features in halves (in chunks of 16)
+        constexpr int FIRST_HALF = ((BN / 16 + 1) / 2) * 16;
+        const int c_begin = warp >= 6 ? FIRST_HALF : 0;
+        const int c_limit = warp >= 6 ? BN : FIRST_HALF;
         uint32_t local = 0;
         for (int item = pair; item < n_items; item += n_pairs, ++local) {
             DD_PAIR_COORDS(item)
             const uint32_t acc = local & 1;
-            const int n = n0 + quarter * 32 + lane;
-            const bool n_ok = n < p.N;
+            const int m = a0 + quarter * 32 + lane;
+            const bool m_ok = m < p.M;
             if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*epilogue_abort) break;
             tc::fence_after_sync();
             const uint32_t lane_addr = tmem_base + acc * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-            for (int c0 = 0; c0 < BN && m0 + c0 < p.M; c0 += 16) {
+            if (b0 + c_begin >= p.N) {                                 // no features for this warp in this tile
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
+            }
+            for (int c0 = c_begin; c0 < c_limit && b0 + c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tc::tmem_ld_x16(lane_addr + c0, r);
+                float res[16];
+                if (m_ok) load_residual_row16(p, m, b0 + c0, res);    // in flight while the accumulator is read
                 tc::tmem_ld_wait();
-                if (c0 + 16 >= BN || m0 + c0 + 16 >= p.M) {           // last read: hand the accumulator back to the leader
+                if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
                 }
-                if (n_ok) {
-                    float accv[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
-                    store_out16(p, m0 + c0, n, accv);
-                }
+                if (m_ok) store_out_row16(p, m, b0 + c0, r, res);
             }
         }
     }
@@ -756,8 +889,9 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int bo
     return 0;
 }
 
+// ma: the operand on the 128 accumulator lanes (the weights, or the tokens for BN >= 128); mb: the other one
 template <int BN>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t s) {
     using C = Config<BN>;
     static bool configured = false;
     if (!configured) {
@@ -765,7 +899,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cu
         if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    const int items = dd_ceil_div(p.N, BM) * dd_ceil_div(p.M, BN) * p.splits;
+    const int items = (C::BY_TOKEN ? dd_ceil_div(p.M, BM) * dd_ceil_div(p.N, BN) : dd_ceil_div(p.N, BM) * dd_ceil_div(p.M, BN)) * p.splits;
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
@@ -773,7 +907,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cu
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    dd_launch(gemm_tcgen05_kernel<BN>, dim3(items < sm_count ? items : sm_count), dim3(THREADS), C::SMEM_BYTES, s, mw, mx, p);
+    dd_launch(gemm_tcgen05_kernel<BN>, dim3(items < sm_count ? items : sm_count), dim3(THREADS_P), C::SMEM_BYTES, s, ma, mb, p);
     return dd_check_launch("dd_gemm_tcgen05");
 }
 
@@ -822,11 +956,11 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    const int items = dd_ceil_div(p.N, 2 * BM) * dd_ceil_div(p.M, BN);
+    const int items = dd_ceil_div(p.M, 2 * BM) * dd_ceil_div(p.N, BN);
     const int pairs = items < sm_count / 2 ? items : sm_count / 2;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(2 * pairs);
-    config.blockDim = dim3(THREADS);
+    config.blockDim = dim3(THREADS_P);
     config.dynamicSmemBytes = C::SMEM_BYTES;
     config.stream = s;
     cudaLaunchAttribute attrs[2];
@@ -853,22 +987,26 @@ DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = 
 // Chooses the token tile, the K split and how the split is reduced (*cluster = 1: inside a thread-block
 // cluster over distributed shared memory; 0: through a global workspace). Returns splits (>= 1).
 DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile, int* cluster) {
-    // Above 64 tokens: the tile among 128, 192 and 256 tokens that needs the least time in whole rounds of one tile
-    // per SM (rounds x tokens per tile); ties go to the smaller tile, which balances better.
+    // Up to 64 tokens the tile is 128 features x 16, 32 or 64 tokens. Above, it is 128 tokens x 128, 192 or 256
+    // features (the value returned in *token_tile is then the feature width).
     int bn = 128;
     if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64;
     else {
-        // Wide outputs (measured at 4800 and 6400 features: 5-10% faster) go to two SMs per 256-feature tile;
-        // with 1600 features the 256-feature tiles waste an eighth of their rows and the one-SM kernel wins.
-        const bool pair = N >= 2048 && cluster != nullptr;
-        const int rows = pair ? 2 * BM : BM, units = pair ? sm_count / 2 : sm_count;
+        // Tiles of 128 tokens x c features on one SM, or of 256 tokens x c features on a pair of SMs (less L2
+        // traffic per flop). A round of one tile per SM was measured to take about as long as c + 64 columns
+        // (2,048 and 4,096 tokens, 1600 to 6400 features), so the choice minimises rounds x (c + 64); ties go to
+        // the pair and to the wider tile.
         long long best = -1;
+        bool pair = false;
         const int candidates[3] = {128, 192, 256};
-        for (int i = 0; i < 3; ++i) {
-            const int c = candidates[i];
-            const long long t = (long long)dd_ceil_div(N, rows) * dd_ceil_div(M, c);
-            const long long cost = (long long)dd_ceil_div(t, units) * c;
-            if (best < 0 || cost < best) { best = cost; bn = c; }
+        for (int two = 0; two <= ((cluster != nullptr && sm_count >= 2) ? 1 : 0); ++two) {
+            const int rows = two ? 2 * BM : BM, units = two ? sm_count / 2 : sm_count;
+            for (int i = 0; i < 3; ++i) {
+                const int c = candidates[i];
+                const long long t = (long long)dd_ceil_div(M, rows) * dd_ceil_div(N, c);
+                const long long cost = (long long)dd_ceil_div(t, units) * (c + 64);
+                if (best < 0 || cost <= best) { best = cost; bn = c; pair = two != 0; }
+            }
         }
         if (token_tile) *token_tile = bn;
         if (cluster) *cluster = pair ? 2 : 0;
@@ -894,11 +1032,12 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
 }
 
 // X [M,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw); bias [N] f32 or null; residual [M,N] f32
-// (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). cluster = 1: splits
-// (at most 8) are the blocks of a cluster and reduce over distributed shared memory (token_tile <= 64);
-// cluster = 2: two SMs per 256-feature tile (tcgen05 cta_group::2), token_tile 128/192/256, no split;
-// cluster = 0 with splits > 1: workspace f32 [splits*M*N] and counters int32 [tiles], zero before the
-// first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
+// (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). token_tile 16/32/64: tiles
+// of 128 features x token_tile tokens; 128/192/256: tiles of 128 tokens x token_tile features, no K split.
+// cluster = 1: splits (at most 8) are the blocks of a cluster and reduce over distributed shared memory
+// (token_tile <= 64); cluster = 2: two SMs per tile of 256 tokens x token_tile features (tcgen05
+// cta_group::2), token_tile 128/192/256; cluster = 0 with splits > 1 (token_tile <= 64): workspace f32
+// [splits*M*N] and counters int32 [tiles], zero before the first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
 // weight matrix of a decode step): this kernel's blocks ask L2 to fetch it while they run.
 DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const float* bias, const float* residual,
                            int ldr, void* out, int ldo, int M, int N, int K, int act, int out_dtype, int splits,
@@ -929,9 +1068,18 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
         if (!workspace || !counters || n_counters < tiles)
             return dd_fail("dd_gemm_tcgen05: split-K needs a workspace and %d counters", tiles);
     }
+    // 16-byte accesses in the epilogue of the 128-token tiles: every row of out, residual and bias must allow them
+    const int out_elem = out_dtype == DD_BF16 ? 2 : 4;
+    p.vec = !((uintptr_t)out & 15) && ((size_t)ldo * out_elem) % 16 == 0 &&
+            (!residual || (!((uintptr_t)residual & 15) && ldr % 4 == 0)) && (!bias || !((uintptr_t)bias & 15));
+    const bool by_token = token_tile >= 128;       // 128 tokens x token_tile features per tile
+    if (by_token && p.splits > 1)
+        return dd_fail("dd_gemm_tcgen05: tiles of 128 tokens take no K split (got %d splits with tile %d)", p.splits, token_tile);
     CUtensorMap mw, mx;
-    if (int e = make_map(&mw, W, N, K, ldw, BM, "the weight matrix")) return e;
-    if (int e = make_map(&mx, X, M, K, ldx, cluster == 2 ? token_tile / 2 : token_tile, "the activations")) return e;
+    const int w_box = by_token ? (cluster == 2 ? token_tile / 2 : token_tile) : BM;
+    const int x_box = by_token ? BM : token_tile;
+    if (int e = make_map(&mw, W, N, K, ldw, w_box, "the weight matrix")) return e;
+    if (int e = make_map(&mx, X, M, K, ldx, x_box, "the activations")) return e;
     cudaStream_t s = (cudaStream_t)stream;
     if (cluster == 2) {
         switch (token_tile) {
@@ -952,9 +1100,9 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
         case 16: return launch<16>(mw, mx, p, s);
         case 32: return launch<32>(mw, mx, p, s);
         case 64: return launch<64>(mw, mx, p, s);
-        case 128: return launch<128>(mw, mx, p, s);
-        case 192: return launch<192>(mw, mx, p, s);
-        case 256: return launch<256>(mw, mx, p, s);
+        case 128: return launch<128>(mx, mw, p, s);
+        case 192: return launch<192>(mx, mw, p, s);
+        case 256: return launch<256>(mx, mw, p, s);
     }
     return dd_fail("dd_gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 192, 256", token_tile);
 }

@@ -57,9 +57,9 @@ def test_epilogues(K, shape):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 5, 13])
-@pytest.mark.parametrize("tile", [16, 64, 192, 256])
+@pytest.mark.parametrize("tile", [16, 32, 64])
 def test_forced_splits_and_tiles(K, splits, tile):
-    a, w, bias, res = operands(40 if tile < 192 else 500, 700, 1600, seed=2)
+    a, w, bias, res = operands(40 if tile < 64 else 150, 700, 1600, seed=2)
     ref = a.double() @ w.double().t() + bias.double()
     out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile)
     again = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile)
@@ -89,9 +89,49 @@ def test_cluster_split(K, splits, tokens, tile):
 
 
 @pytest.mark.parametrize("tile", [128, 192, 256])
-@pytest.mark.parametrize("shape", [(300, 257, 1608), (2048, 1600, 1600), (1000, 4800, 320), (130, 515, 64)])
+@pytest.mark.parametrize("shape", [(300, 520, 200), (129, 257, 1608), (65, 50257, 64), (700, 1600, 320)])
+def test_token_lane_tiles(K, tile, shape):
+    """Tiles of 128 tokens x tile features (one SM): rows moved in 16-byte pieces where every row start allows it,
+    element by element at a ragged last chunk (520 = 32 x 16 + 8), with rows that are not 16-byte aligned (257
+    floats), a bias or an output that starts off a 16-byte boundary, and an output inside a wider buffer."""
+    M, N, Kd = shape
+    a, w, bias, res = operands(M, N, Kd, seed=7)
+    ref = a.double() @ w.double().t() + bias.double()
+    tol = 5e-4 * math.sqrt(Kd / 64)
+    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=1, token_tile=tile, cluster=0)
+    assert (out.double() - ref).abs().max() < tol
+    shifted = torch.zeros(N + 1, device=DEV)
+    shifted[1:] = bias
+    assert torch.equal(out, K.gemm_tcgen05(a, w, shifted[1:], out_dtype=torch.float32, splits=1, token_tile=tile, cluster=0))
+    wide = torch.full((M, N + 24), 7.0, device=DEV)
+    K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, out=wide[:, 8:8 + N], splits=1, token_tile=tile, cluster=0)
+    assert torch.equal(wide[:, 8:8 + N], out) and bool((wide[:, :8] == 7).all()) and bool((wide[:, 8 + N:] == 7).all())
+    odd = torch.full((M, N + 3), 7.0, device=DEV)
+    K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, out=odd[:, 1:1 + N], splits=1, token_tile=tile, cluster=0)
+    assert torch.equal(odd[:, 1:1 + N], out) and bool((odd[:, :1] == 7).all()) and bool((odd[:, 1 + N:] == 7).all())
+    stream = res.clone()
+    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream, splits=1, token_tile=tile, cluster=0)
+    assert (stream.double() - (ref + res.double())).abs().max() < tol
+    half = K.gemm_tcgen05(a, w, bias, splits=1, token_tile=tile, cluster=0)
+    assert half.dtype == torch.bfloat16 and (half.double() - ref).abs().max() < 2.0 ** -8 * float(ref.abs().max()) + 1e-3
+    half_wide = torch.full((M, N + 24), 7.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tcgen05(a, w, bias, out=half_wide[:, 8:8 + N], splits=1, token_tile=tile, cluster=0)
+    assert torch.equal(half_wide[:, 8:8 + N], half) and bool((half_wide[:, :8] == 7).all()) and bool((half_wide[:, 8 + N:] == 7).all())
+    gelu = K.gemm_tcgen05(a, w, bias, activation="gelu_new", splits=1, token_tile=tile, cluster=0)
+    want = 0.5 * ref * (1 + torch.tanh(math.sqrt(2 / math.pi) * (ref + 0.044715 * ref ** 3)))
+    assert (gelu.double() - want).abs().max() < 2.0 ** -7 * float(want.abs().max()) + 1e-3
+    erf = K.gemm_tcgen05(a, w, bias, activation="gelu", out_dtype=torch.float32, splits=1, token_tile=tile, cluster=0)
+    assert (erf.double() - 0.5 * ref * (1 + torch.erf(ref / math.sqrt(2)))).abs().max() < tol
+    assert K.read_error_flag(DEV) == 0
+    if Kd >= 128:
+        with pytest.raises(K.KernelError, match="no K split"):
+            K.gemm_tcgen05(a, w, bias, splits=2, token_tile=tile, cluster=0)
+
+
+@pytest.mark.parametrize("tile", [128, 192, 256])
+@pytest.mark.parametrize("shape", [(300, 257, 1608), (2048, 1600, 1600), (1000, 4800, 320), (130, 520, 64)])
 def test_two_sms_per_tile(K, tile, shape):
-    """tcgen05 cta_group::2: a cluster of two blocks on one 256-feature tile, every epilogue."""
+    """tcgen05 cta_group::2: a cluster of two blocks on one tile of 256 tokens, every epilogue."""
     M, N, Kd = shape
     a, w, bias, res = operands(M, N, Kd, seed=6)
     ref = a.double() @ w.double().t() + bias.double()
