@@ -1,0 +1,426 @@
+// Prompt-portion attention on the tcgen05 tensor cores, for bfloat16 caches and head size 64.
+//
+// A block owns 128 consecutive query tokens of one request and one head and walks the request's keys in blocks
+// of 128 straight out of the cache pages. Three roles:
+//   warp 0      TMA: the query tile once, then per key block one box per cache page for the keys and one for
+//               the values (each lane issues the boxes of one page), several blocks ahead;
+//   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, accumulator in TMEM, two buffers so that the
+//               scores of block j+2 are computed while the softmax works on j and j+1), then O_j = P_j V_j
+//               (128 x 64) from the probabilities that the softmax warps left in shared memory; V is read as it
+//               lies in the cache, as an MN-major operand;
+//   warps 2..5  softmax: a thread owns one query row (its TMEM lane), so the running maximum and sum need no
+//               shuffles; it takes the 128 scores of a block into registers with four TMEM loads in flight,
+//               writes P as bfloat16 in the swizzled K-major layout the MMA reads, and keeps the output
+//               row in registers: O = (O + P_{j-1} V_{j-1}) * exp2(m_{j-1} - m_j), float32 throughout.
+// Scores, softmax and the weighted sum of values are float32 (damendaemon/kernels.py:147-178 for the mask and
+// the stable softmax; damendaemon/qwen2.py:754-770 for the offset-aware causal rule). Keys outside the live
+// range (beyond the last query of the tile, before the window, pages that were given back) are never multiplied
+// in: their scores are replaced, not scaled, and their value rows are zeroed in shared memory, so that stale
+// cache contents of any bit pattern cannot reach the result.
+// Every wait is bounded; a wait that runs out sets the error flag and the block leaves through the common exit.
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include <math_constants.h>
+
+namespace {
+constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 192, STAGES = 4;
+constexpr int TILE_BYTES = BKV * D * 2;             // one 128 x 64 bf16 tile: 16 KB
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // keys, then values
+constexpr int P_BYTES = 2 * TILE_BYTES;             // 128 x 128 probabilities as two 64-key halves
+constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O_j: 2 x 64 columns
+constexpr int S_COL = 0, O_COL = 256;
+
+struct AttnParams {
+    const int* entry_start;
+    const int* entry_pos0;
+    const int* block_table;
+    __nv_bfloat16* out;
+    int* error_flag;
+    int n_entries, max_blocks, out_stride, H, KH, P, n_pages, window;
+    float scale_log2e;
+    unsigned long long* timeline;   // null, or 64 time stamps (ns) per block: where a block's time goes
+};
+
+unsigned long long* g_timeline = nullptr;
+
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 const AttnParams p) {
+    // which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once.
+    int e = 0, tile = blockIdx.x, len = 0;
+    for (; e < p.n_entries; ++e) {
+        len = p.entry_start[e + 1] - p.entry_start[e];
+        const int nt = (len + BQ - 1) / BQ;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (e == p.n_entries) return;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sQ = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sKV = sQ + TILE_BYTES;
+    uint8_t* sP = sKV + STAGES * STAGE_BYTES;
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
+    uint64_t* kv_empty = kv_full + STAGES;
+    uint64_t* q_full = kv_empty + STAGES;
+    uint64_t* s_full = q_full + 1;        // [2]
+    uint64_t* p_ready = s_full + 2;       // [2]
+    uint64_t* o_full = p_ready + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, kh = h / (p.H / p.KH);
+    const int q0 = tile * BQ;
+    const int rows = min(BQ, len - q0);
+    const int row0 = p.entry_start[e] + q0;
+    const int pos_first = p.entry_pos0[e] + q0, pos_last = pos_first + rows - 1;
+    const int kv_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int kb_first = kv_lo / BKV * BKV;
+    const int n_blocks = (pos_last - kb_first) / BKV + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&kv_full[s], 1);
+            tc::mbar_init(&kv_empty[s], 1);
+        }
+        tc::mbar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&s_full[b], 1);
+            tc::mbar_init(&p_ready[b], 4);        // one arrival per softmax warp
+            tc::mbar_init(&o_full[b], 1);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    unsigned long long* stamps = p.timeline ? p.timeline + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 64 : nullptr;
+    if (stamps && threadIdx.x == 0) stamps[0] = tc::global_ns();
+    dd_launch_dependents();
+    dd_grid_wait();              // queries and the cache are earlier kernels' results
+    if (stamps && threadIdx.x == 0) stamps[1] = tc::global_ns();
+
+    if (warp == 0) {
+        // ---- TMA ----
+        if (lane == 0) {
+            tc::prefetch_tensormap(&map_q);
+            tc::prefetch_tensormap(&map_kv);
+            tc::mbar_expect_tx(q_full, TILE_BYTES);
+            tc::tma_load_2d(sQ, &map_q, h * D, row0, q_full);       // rows past the last token read as zeros
+        }
+        const int pages_per_block = BKV / p.P;
+        const int* bt = p.block_table + (size_t)e * p.max_blocks;
+        const uint32_t page_bytes = (uint32_t)p.P * D * 2;
+        // The warp holds 32 consecutive entries of the request's block table, one per lane, and the next 32 already
+        // requested: a key block's pages never straddle such a window (its first entry is a multiple of the pages
+        // per block, which divide 32), and no block waits for a table read of its own.
+        auto table_window = [&](int w) { const int i = w * 32 + lane; return i < p.max_blocks ? bt[i] : -1; };
+        int window_at = (kb_first / p.P) / 32;
+        int held = table_window(window_at), ahead = table_window(window_at + 1);
+        for (int j = 0; j < n_blocks; ++j) {
+            const int s = j % STAGES;
+            if (j >= STAGES) {
+                bool ok = true;
+                if (lane == 0) ok = tc::mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, abort_flag);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+            }
+            const int kb = kb_first + j * BKV;
+            uint8_t* k_dst = sKV + s * STAGE_BYTES;
+            uint8_t* v_dst = k_dst + TILE_BYTES;
+            const int first_entry = kb / p.P;
+            if (first_entry / 32 != window_at) {
+                window_at = first_entry / 32;
+                held = ahead;
+                ahead = table_window(window_at + 1);
+            }
+            const int page = __shfl_sync(0xffffffffu, held, (first_entry + lane) & 31);
+            bool valid = false;
+            if (lane < pages_per_block) {
+                const int key0 = kb + lane * p.P;
+                valid = key0 <= pos_last && key0 + p.P > kv_lo;
+                if (valid && (page < 0 || page >= p.n_pages)) {
+                    atomicOr(p.error_flag, 4);
+                    valid = false;
+                }
+            }
+            const int n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+            if (lane < pages_per_block) {
+                if (valid) {
+                    const int k_row = ((page * 2 + 0) * p.KH + kh) * p.P;
+                    const int v_row = ((page * 2 + 1) * p.KH + kh) * p.P;
+                    tc::tma_load_2d(k_dst + lane * page_bytes, &map_kv, 0, k_row, &kv_full[s]);
+                    tc::tma_load_2d(v_dst + lane * page_bytes, &map_kv, 0, v_row, &kv_full[s]);
+                } else {
+                    // no live key in this page: its scores are all masked; its value rows must be zeros
+                    uint4* z = reinterpret_cast<uint4*>(v_dst + lane * page_bytes);
+                    for (uint32_t i = 0; i < page_bytes / 16; ++i) z[i] = make_uint4(0, 0, 0, 0);
+                    tc::fence_proxy_async();
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_expect_tx(&kv_full[s], (uint32_t)n_valid * 2 * page_bytes);
+            if (stamps && lane == 0 && j < 8) stamps[56 + j] = tc::global_ns();
+        }
+    } else if (warp == 1) {
+        // ---- MMA ----
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc_s = tc::idesc_bf16_f32(BQ, BKV);
+            constexpr uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(BQ, D);
+            const uint32_t q_addr = tc::smem_u32(sQ);
+            bool ok = tc::mbar_wait(q_full, 0, abort_flag);
+            tc::fence_after_sync();
+            auto issue_scores = [&](int j) {
+                const int s = j % STAGES;
+                if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) { ok = false; return; }
+                tc::fence_after_sync();
+                const uint32_t k_addr = tc::smem_u32(sKV + s * STAGE_BYTES);
+                const uint32_t tmem_s = tmem_base + S_COL + (j & 1) * BKV;
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k)
+                    tc::mma_bf16(tmem_s, tc::smem_desc_sw128(q_addr + k * 32), tc::smem_desc_sw128(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
+                tc::mma_commit(&s_full[j & 1]);
+            };
+            if (ok) issue_scores(0);
+            if (ok && n_blocks > 1) issue_scores(1);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j % STAGES, b = j & 1;
+                if (!tc::mbar_wait(&p_ready[b], (j >> 1) & 1, abort_flag)) break;
+                tc::fence_after_sync();
+                if (stamps && j < 8) stamps[40 + 2 * j] = tc::global_ns();
+                const uint32_t v_addr = tc::smem_u32(sKV + s * STAGE_BYTES + TILE_BYTES);
+                const uint32_t p_addr = tc::smem_u32(sP + b * P_BYTES);
+                const uint32_t tmem_o = tmem_base + O_COL + b * D;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)
+                    tc::mma_bf16(tmem_o, tc::smem_desc_sw128(p_addr + (k / 4) * TILE_BYTES + (k % 4) * 32),
+                                 tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o, k > 0 ? 1u : 0u);
+                tc::mma_commit(&o_full[b]);
+                tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
+                if (j + 2 < n_blocks) issue_scores(j + 2);   // its score buffer is free: P_j exists
+                if (stamps && j < 8) stamps[41 + 2 * j] = tc::global_ns();
+            }
+        }
+    } else {
+        // ---- softmax and output: thread = query row = TMEM lane ----
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int qpos = pos_first + r;
+        const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        float m = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int b = j & 1, kb = kb_first + j * BKV;
+            if (!tc::mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc::fence_after_sync();
+            const bool stamp = stamps && threadIdx.x == 64 && j < 8;
+            if (stamp) stamps[8 + 4 * j] = tc::global_ns();
+            const uint32_t s_addr = lane_addr + S_COL + b * BKV;
+            const bool need_mask = kb + BKV - 1 > qpos || kb < qlo;
+            // the whole row of this block's scores: four loads in flight, one wait
+            uint32_t sv[BKV];
+#pragma unroll
+            for (int c0 = 0; c0 < BKV; c0 += 32) tc::tmem_ld_x32(s_addr + c0, sv + c0);
+            tc::tmem_ld_wait();
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BKV; ++i)
+                    if (kb + i > qpos || kb + i < qlo) sv[i] = 0xff800000u;      // -inf: replaced, whatever was there
+            }
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (stamp) stamps[9 + 4 * j] = tc::global_ns();
+            const float m_new = fmaxf(m, mx * p.scale_log2e);      // the scale is positive
+            const float alpha = m_new == -CUDART_INF_F ? 1.f : exp2_approx(m - m_new);
+            const float msub = m_new == -CUDART_INF_F ? 0.f : m_new;
+            m = m_new;
+            // exponentials (a masked score gives exactly 0), their sum, P as bfloat16 into shared memory (K-major,
+            // 128-byte swizzle: 16-byte chunk c of row r lies at chunk c ^ (r & 7))
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint8_t* p_row = sP + b * P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < BKV / 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = exp2_approx(fmaf(__uint_as_float(sv[8 * c + 2 * i]), p.scale_log2e, -msub));
+                    const float p1 = exp2_approx(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), p.scale_log2e, -msub));
+                    sum4[i] += p0 + p1;
+                    w[i] = pack_bf16(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(p_row + (c / 8) * TILE_BYTES + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            l = l * alpha + sum;
+            if (kb + BKV - 1 > pos_last) {
+                // value rows of keys past the tile's last query: unwritten cache slots, to be zeros under P = 0
+                const int s = j % STAGES;
+                if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) { ok = false; break; }
+                if (kb + r > pos_last) {
+                    uint4* z = reinterpret_cast<uint4*>(sKV + s * STAGE_BYTES + TILE_BYTES + r * 128);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) z[i] = make_uint4(0, 0, 0, 0);
+                }
+            }
+            tc::fence_proxy_async();          // P (and the zeroed rows) to the proxy the MMA reads through
+            tc::fence_before_sync();          // this thread's TMEM reads of S are done
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&p_ready[b]);
+            if (stamp) stamps[10 + 4 * j] = tc::global_ns();
+            if (j > 0) {
+                // O = (O + P_{j-1} V_{j-1}) * alpha_j
+                const int pb = (j - 1) & 1;
+                if (!tc::mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc::fence_after_sync();
+                uint32_t v[32];
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + c0, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + __uint_as_float(v[i])) * alpha;
+                }
+            }
+            if (stamp) stamps[11 + 4 * j] = tc::global_ns();
+        }
+        if (ok) {
+            const int pb = (n_blocks - 1) & 1;
+            ok = tc::mbar_wait(&o_full[pb], ((n_blocks - 1) >> 1) & 1, abort_flag);
+            if (ok) {
+                tc::fence_after_sync();
+                uint32_t v[32];
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + c0, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
+                }
+                if (r < rows) {
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * D;
+#pragma unroll
+                    for (int c = 0; c < D; c += 8)
+                        *reinterpret_cast<uint4*>(dst + c) =
+                            make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
+                                       pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
+                }
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 8);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+// rows x cols bf16 with row stride ld elements; boxes of box_rows x 64 columns, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, unsigned long long rows, int cols, long long ld, int box_rows, const char* what) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return dd_fail("dd_attention_prefill_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return dd_fail("dd_attention_prefill_tcgen05: cannot describe %s to TMA (driver error %d)", what, (int)r);
+    return 0;
+}
+}  // namespace
+
+// Debugging aid: a device buffer of 64 time stamps (ns) per block of the next launches, null switches it off:
+// 0 start, 1 inputs ready; for the first eight key blocks j: 8+4j scores there, 9+4j maximum known, 10+4j P handed
+// over, 11+4j output row updated (thread 64); 40+2j P seen by the MMA thread, 41+2j its MMAs issued; 56+j loads issued.
+DD_API void dd_attention_prefill_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
+
+// Head size 64, pages of 8, 16, 32, 64 or 128 tokens (a page is one TMA box inside a 128-key block).
+DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, int head_dim, int page_size, int dtype) {
+    return dtype == DD_BF16 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim == D &&
+           (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
+}
+
+// The arguments of dd_attention_prefill: entries are runs of consecutive tokens of one request; entry e holds
+// flattened tokens entry_start[e] .. entry_start[e+1]-1 at positions entry_pos0[e] ...; block_table row e is its
+// pages. cache [n_pages, 2, n_kv_heads, page_size, 64] bf16.
+DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* cache, const int* entry_start,
+                                        const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
+                                        int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
+                                        int head_dim, int page_size, int n_pages, int window, float scale,
+                                        int* error_flag, void* stream) {
+    if (n_tokens <= 0 || n_entries <= 0) return 0;
+    if (!dd_attention_prefill_tcgen05_supported(n_heads, n_kv_heads, head_dim, page_size, DD_BF16))
+        return dd_fail("dd_attention_prefill_tcgen05: needs head size 64, pages of 8 to 128 tokens (a power of two) and heads a "
+                       "multiple of key/value heads (got head size %d, pages of %d, %d and %d heads)",
+                       head_dim, page_size, n_heads, n_kv_heads);
+    if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
+        return dd_fail("dd_attention_prefill_tcgen05: rows must be 16-byte aligned");
+    if (n_heads > 65535) return dd_fail("dd_attention_prefill_tcgen05: too many heads");
+    if (!(scale > 0.f)) return dd_fail("dd_attention_prefill_tcgen05: the score scale must be positive");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return dd_fail("dd_attention_prefill_tcgen05: shared memory of %d bytes refused: %s", SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_q, map_kv;
+    if (int e = make_map(&map_q, q, (unsigned long long)n_tokens, n_heads * D, q_stride, BQ, "the queries")) return e;
+    const unsigned long long kv_rows = (unsigned long long)n_pages * 2 * n_kv_heads * page_size;
+    if (int e = make_map(&map_kv, cache, kv_rows, D, D, page_size, "the cache")) return e;
+    AttnParams p;
+    p.entry_start = entry_start; p.entry_pos0 = entry_pos0; p.block_table = block_table;
+    p.out = (__nv_bfloat16*)out; p.error_flag = error_flag;
+    p.n_entries = n_entries; p.max_blocks = max_blocks; p.out_stride = out_stride; p.H = n_heads; p.KH = n_kv_heads;
+    p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
+    p.timeline = g_timeline;
+    // an upper bound of the number of 128-row tiles; blocks beyond the real count return at once
+    dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, n_heads);
+    dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, p);
+    return dd_check_launch("dd_attention_prefill_tcgen05");
+}

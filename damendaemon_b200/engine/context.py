@@ -51,7 +51,12 @@ class StepContext:
                                             k_new=k if cache.writable else None, v_new=v if cache.writable else None)
         if cache.writable:
             kernels.kv_store(k, v, self.token_entry, self.positions, table, kv)
-        if not self.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
-            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
+        if not self.decode_only and fast:
+            if self.runtime.attention != "mma" and \
+                    kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype):
+                return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window,
+                                                 kernel="tcgen05")
+            if kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
+                return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                       n_splits=self.key_splits(n_heads))

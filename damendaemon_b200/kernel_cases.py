@@ -58,17 +58,18 @@ def _decode_case(batch, context, dev):
     return run, {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
 
 
-def _prefill_case(prompts, length, dev):
+def _prefill_case(prompts, length, dev, kernel="tcgen05"):
     caches, table = _cache_case(prompts, length, dev, 4)
     start = torch.arange(prompts + 1, dtype=torch.int32, device=dev) * length
     pos0 = torch.zeros(prompts, dtype=torch.int32, device=dev)
     q = torch.randn(prompts * length, H * D, device=dev).to(torch.bfloat16)
-    run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None)
+    run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None, kernel=kernel)
     return run, {"bytes": prompts * length * H * D * 6, "flops": prompts * 4 * (length * (length + 1) // 2) * H * D}
 
 
 def build(name, device="cuda:0"):
-    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> | attn_prefill"""
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> | attn_prefill | attn_prefill_mma |
+    attn_prefill_long (one prompt of 4,096 tokens)"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
@@ -77,6 +78,12 @@ def build(name, device="cuda:0"):
         return _decode_case(int(name[len("attn_decode_b"):]), 768, device)
     if name == "attn_prefill":
         return _prefill_case(2, 1024, device)
+    if name == "attn_prefill_mma":
+        return _prefill_case(2, 1024, device, kernel="mma")
+    if name == "attn_prefill_long":
+        return _prefill_case(1, 4096, device)
+    if name == "attn_prefill_long_mma":
+        return _prefill_case(1, 4096, device, kernel="mma")
     raise ValueError(f"unknown kernel case {name!r}")
 
 

@@ -43,6 +43,9 @@ _SIGNATURES = {
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void],
+        "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
+        "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
+                                        + [_c_int] * 6 + [_c_float, _c_void, _c_void],
         "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
                                 _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 8
@@ -363,9 +366,16 @@ def attention_prefill_supported(n_heads, kv_heads, head_dim, dtype):
     return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_prefill_supported(n_heads, kv_heads, head_dim, BF16))
 
 
-def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, scale, window=None, out=None):
+def attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, dtype):
+    return dtype == torch.bfloat16 and bool(
+        library("tensor").dd_attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, BF16))
+
+
+def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, scale, window=None, out=None, kernel="mma"):
     """Tensor-core attention for runs of consecutive tokens (prompt portions; a decoded token is a run of one)
-    over a bfloat16 cache. entry_start: int32 [E+1], entry_pos0: int32 [E]; see attention_prefill_supported."""
+    over a bfloat16 cache. entry_start: int32 [E+1], entry_pos0: int32 [E]. kernel: 'mma' (mma.sync tiles of 64
+    queries, see attention_prefill_supported) or 'tcgen05' (tiles of 128 queries with TMA and TMEM accumulators,
+    see attention_prefill_tcgen05_supported)."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n, n_entries = q.shape[0], entry_pos0.numel()
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
@@ -373,7 +383,9 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
         raise KernelError("attention_prefill: q or the entry arrays do not fit the cache")
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
-    _call(library("tensor"), "dd_attention_prefill", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+    if kernel not in ("mma", "tcgen05"):
+        raise KernelError(f"attention_prefill: unknown kernel {kernel!r}")
+    _call(library("tensor"), "dd_attention_prefill" + ("_tcgen05" if kernel == "tcgen05" else ""), _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
           _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           n_heads, kv_heads, head_dim, page_size, n_pages, 0 if window is None else int(window), float(scale),

@@ -39,7 +39,7 @@ class Runtime:
     dtype: torch.dtype            # engine dtype: torch.bfloat16 or torch.float32
     device: torch.device
     gemm: str = "auto"            # 'auto' | 'simt' | 'tcgen05'
-    attention: str = "auto"       # 'auto' | 'rows'
+    attention: str = "auto"       # 'auto' | 'mma' (no tcgen05 prompt kernel) | 'rows' (the general kernel only)
     fuse: bool = False            # let parts take their fused multi-part kernels (decode feed-forward with its norm:
                                   # measured slower than the separate kernels on B200 so far, hence off)
 

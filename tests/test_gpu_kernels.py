@@ -214,6 +214,32 @@ def test_attention_prefill_bf16(K, d, heads, kv_heads, page, window):
     assert (out.float() - rows.float()).abs().max() < tol(torch.bfloat16)
 
 
+@pytest.mark.parametrize("heads,kv_heads,page", [(5, 5, 16), (6, 1, 32), (4, 2, 8), (3, 3, 128), (2, 1, 64)])
+@pytest.mark.parametrize("window", [None, 70, 300])
+def test_attention_prefill_tcgen05(K, heads, kv_heads, page, window):
+    """The tcgen05 kernel (tiles of 128 queries, TMA boxes per cache page, accumulators in TMEM): whole prompts
+    that end inside a page, a portion that continues cached keys, single tokens, more key blocks than the ring has
+    stages, a far key, a poisoned cache around the live keys."""
+    K.library("tensor")
+    assert K.attention_prefill_tcgen05_supported(heads, kv_heads, 64, page, torch.bfloat16)
+    assert not K.attention_prefill_tcgen05_supported(heads, kv_heads, 128, page, torch.bfloat16)
+    assert not K.attention_prefill_tcgen05_supported(heads, kv_heads, 64, 48, torch.bfloat16)
+    lengths, new = [150, 1, 365, 64, 1300, 65, 900, 129], [150, 1, 65, 64, 1300, 3, 130, 128]
+    c = paged_case(K, torch.bfloat16, heads, kv_heads, 64, page, lengths=lengths, new=new, window=window, n_splits=1,
+                   spike=3 if window is None else None)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    entry_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    entry_pos0 = torch.tensor([L - n for L, n in zip(lengths, new)], dtype=torch.int32, device=DEV)
+    out = K.attention_prefill(c["q"], c["cache"], entry_start, entry_pos0, c["table"], heads, c["scale"], window, kernel="tcgen05")
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    rows = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window)
+    assert (out.float() - rows.float()).abs().max() < tol(torch.bfloat16)
+
+
 def test_attention_rejects_bad_sizes(K):
     cache = torch.zeros(4, 2, 2, 16, 20, device=DEV)
     q = torch.zeros(1, 40, device=DEV)
