@@ -54,6 +54,21 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
 }
 
+// Debugging aid (dd_attention_decode_stamps): 16 time stamps (ns) per block, written by its first thread: 0 start,
+// 1 inputs ready, 2 first copies issued, 3.. the first eight tiles begin, 11 last tile done, 12 block's result
+// written, 13 splits merged (only in the block that merges).
+__device__ unsigned long long* g_stamps = nullptr;
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define STAMP(i)                                                                                                      \
+    do {                                                                                                              \
+        if (g_stamps && threadIdx.x == 0)                                                                             \
+            g_stamps[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (i)] = now_ns(); \
+    } while (0)
+
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* k_new,
@@ -72,9 +87,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     __shared__ float sh_o[WARPS][D];
     __shared__ float sh_ml[WARPS][2];
     __shared__ int sh_last;
+    STAMP(0);
     dd_launch_dependents();
-    dd_grid_wait();
 
+    // Positions, entries and the block table are this step's inputs, not an earlier kernel's results: they are read,
+    // and the table lines of this block's keys brought into L1, while the kernel before this one is still running.
     const int split = blockIdx.x, n_splits = gridDim.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = lane % C, kg = lane / C;
@@ -86,6 +103,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     per = (per + TILE - 1) / TILE * TILE;
     const int k0 = lo + split * per;
     const int k1 = min(hi, k0 + per);
+    const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
+    for (int blk = k0 / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + min(blk, max_blocks - 1)));
+    dd_grid_wait();
+    STAMP(1);
 
     // the query as the A operand: row 0 of a 16-row tile, every other row zero
     uint32_t qf[KS][4];
@@ -99,7 +121,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             qf[ks][3] = 0u;
         }
     }
-    const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
     const size_t head_plane = (size_t)P * D;
     const size_t page_stride = 2 * (size_t)H * head_plane;       // key/value heads = heads here
     const size_t k_off = (size_t)h * head_plane + c * 8;
@@ -109,7 +130,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     // tiles of this warp: base = k0 + (warp + i * WARPS) * TILE
     const int first_key = k0 + warp * TILE;
     const int n_tiles = first_key < k1 ? (k1 - first_key + WARPS * TILE - 1) / (WARPS * TILE) : 0;
-    auto issue = [&](int i) {
+    // The cache pages of the rows this lane copies in tile i, looked up apart from the copies: the copies are
+    // ordered (asm volatile), and with a table read in front of each, a tile cost four trips to L2 in a row,
+    // about 1 us, which bounded the whole kernel. The next tile's pages are requested a tile ahead.
+    auto lookup = [&](int i, int* pages) {
+        const int base = first_key + i * WARPS * TILE;
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+            const int key = base + s * KPL + kg;
+            const int blk = key / P;
+            pages[s] = (key < k1 && blk < max_blocks) ? bt[blk] : -1;
+        }
+    };
+    auto issue = [&](int i, const int* pages) {
         uint8_t* kt = my_ring + (i % STAGES) * 2 * TILE_BYTES;
         uint8_t* vt = kt + TILE_BYTES;
         const int base = first_key + i * WARPS * TILE;
@@ -118,36 +151,28 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             const int row = s * KPL + kg;
             const int key = base + row;
             const uint32_t off = tile_off<D>(row, c);
+            const int page = pages[s];
             bool ok = key < k1;
+            if (ok && (page < 0 || page >= n_pages)) {
+                atomicOr(error_flag, k_new != nullptr && key == pos ? 2 : 4);
+                ok = false;
+            }
             if (ok && k_new != nullptr && key == pos) {
                 // this step's own key and value: from the projection's output, and into the cache
                 const __nv_bfloat16* ks = k_new + (size_t)t * q_stride + (size_t)h * D + c * 8;
                 const __nv_bfloat16* vs = v_new + (size_t)t * q_stride + (size_t)h * D + c * 8;
                 cp_async16(kt + off, ks);
                 cp_async16(vt + off, vs);
-                const int blk = key / P;
-                const int page = blk < max_blocks ? bt[blk] : -1;
-                if (page < 0 || page >= n_pages) atomicOr(error_flag, 2);
-                else {
-                    const size_t dst = (size_t)page * page_stride + (size_t)(key % P) * D;
-                    *reinterpret_cast<uint4*>(cache + dst + k_off) = *reinterpret_cast<const uint4*>(ks);
-                    *reinterpret_cast<uint4*>(cache + dst + v_off) = *reinterpret_cast<const uint4*>(vs);
-                }
+                const size_t dst = (size_t)page * page_stride + (size_t)(key % P) * D;
+                *reinterpret_cast<uint4*>(cache + dst + k_off) = *reinterpret_cast<const uint4*>(ks);
+                *reinterpret_cast<uint4*>(cache + dst + v_off) = *reinterpret_cast<const uint4*>(vs);
                 continue;
             }
             if (ok) {
-                const int blk = key / P;
-                const int page = blk < max_blocks ? bt[blk] : -1;
-                if (page < 0 || page >= n_pages) {
-                    atomicOr(error_flag, 4);
-                    ok = false;
-                } else {
-                    const size_t src = (size_t)page * page_stride + (size_t)(key % P) * D;
-                    cp_async16(kt + off, cache + src + k_off);
-                    cp_async16(vt + off, cache + src + v_off);
-                }
-            }
-            if (!ok) {          // keys beyond the range are masked by their index; their rows must still be finite
+                const size_t src = (size_t)page * page_stride + (size_t)(key % P) * D;
+                cp_async16(kt + off, cache + src + k_off);
+                cp_async16(vt + off, cache + src + v_off);
+            } else {            // keys beyond the range are masked by their index; their rows must still be finite
                 *reinterpret_cast<uint4*>(kt + off) = make_uint4(0, 0, 0, 0);
                 *reinterpret_cast<uint4*>(vt + off) = make_uint4(0, 0, 0, 0);
             }
@@ -158,12 +183,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
     for (int i = 0; i < C; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 #pragma unroll
+    int pages[STAGES][STEPS];          // of the tiles about to be issued; the loop below is unrolled over its slots
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) lookup(i, pages[i]);
+#pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        if (i < n_tiles) issue(i);
+        if (i < n_tiles) issue(i, pages[i]);
         cp_commit();
     }
+    STAMP(2);
     for (int i = 0; i < n_tiles; ++i) {
-        if (i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
+        if (i < 8) STAMP(3 + i);
+        if (i + STAGES - 1 < n_tiles) issue(i + STAGES - 1, pages[STAGES - 1]);
+        // slide: the next tile to issue is i + STAGES, its pages come while this tile is computed
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) pages[STAGES - 1][s] = -1;
+        if (i + STAGES < n_tiles) lookup(i + STAGES, pages[STAGES - 1]);
         cp_commit();
         cp_wait<STAGES - 1>();
         __syncwarp();                                   // other lanes' copies and zero fills are visible
@@ -220,6 +255,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         __syncwarp();                                   // the stage may be refilled
     }
     cp_wait<0>();
+    STAMP(11);
     // row 0: lanes 0..3 hold dims 8j + 2*t4 + {0,1}; their sums of l differ by the keys each saw
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
@@ -247,6 +283,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (n_splits == 1) out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         else part_o[item * D + d] = acc;
     }
+    STAMP(12);
     if (n_splits == 1) return;
     if (threadIdx.x == 0) { part_ml[2 * item] = M; part_ml[2 * item + 1] = L; }
     __threadfence();
@@ -258,25 +295,47 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     __syncthreads();
     if (!sh_last) return;
     __threadfence();
+    // Thread d merges output dimension d. The partial maxima, sums and outputs of eight splits are requested
+    // together and merged with a running maximum, so the tail costs one trip to L2 per eight splits.
     const size_t first = ((size_t)t * H + h) * n_splits;
-    float Mx = -CUDART_INF_F;
-    for (int sp = 0; sp < n_splits; ++sp) Mx = fmaxf(Mx, __ldcg(part_ml + 2 * (first + sp)));
-    float Lx = 0.f;
-    for (int sp = 0; sp < n_splits; ++sp) {
-        const float ls = __ldcg(part_ml + 2 * (first + sp) + 1);
-        if (ls > 0.f) Lx += ls * exp2f(__ldcg(part_ml + 2 * (first + sp)) - Mx);
-    }
     for (int d = threadIdx.x; d < D; d += WARPS * 32) {
-        float acc = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float ls = __ldcg(part_ml + 2 * (first + sp) + 1);
-            if (ls > 0.f) acc += __ldcg(part_o + (first + sp) * D + d) * exp2f(__ldcg(part_ml + 2 * (first + sp)) - Mx);
+        float Mx = -CUDART_INF_F, Lx = 0.f, acc = 0.f;
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float mm[8], ll[8], oo[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool live = sp0 + u < n_splits;
+                const size_t it = first + sp0 + (live ? u : 0);
+                mm[u] = live ? __ldcg(part_ml + 2 * it) : -CUDART_INF_F;
+                ll[u] = live ? __ldcg(part_ml + 2 * it + 1) : 0.f;
+                oo[u] = live ? __ldcg(part_o + it * D + d) : 0.f;
+            }
+            float cm = Mx;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (ll[u] > 0.f) cm = fmaxf(cm, mm[u]);
+            if (cm == -CUDART_INF_F) continue;            // nothing live so far
+            const float keep = Mx == -CUDART_INF_F ? 0.f : exp2f(Mx - cm);
+            acc *= keep;
+            Lx *= keep;
+            Mx = cm;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (ll[u] > 0.f) {
+                    const float w = exp2f(mm[u] - Mx);
+                    Lx += ll[u] * w;
+                    acc += oo[u] * w;
+                }
         }
         out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx : 0.f);
     }
     if (threadIdx.x == 0) counters[t * H + h] = 0;
+    STAMP(13);
 }
 }  // namespace
+
+// A device buffer of 16 stamps per block of the following launches; null switches the stamps off.
+DD_API void dd_attention_decode_stamps(unsigned long long* buffer) { cudaMemcpyToSymbol(g_stamps, &buffer, sizeof(buffer)); }
 
 // Returns 1 if dd_attention_decode takes this problem, else 0 (use dd_attention_rows).
 DD_API int dd_attention_decode_supported(int n_heads, int n_kv_heads, int head_dim, int dtype) {
