@@ -182,7 +182,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     float m = -CUDART_INF_F, l = 0.f, o[C][4];
 #pragma unroll
     for (int i = 0; i < C; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-#pragma unroll
     int pages[STAGES][STEPS];          // of the tiles about to be issued; the loop below is unrolled over its slots
 #pragma unroll
     for (int i = 0; i < STAGES; ++i) lookup(i, pages[i]);
