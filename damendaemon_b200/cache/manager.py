@@ -105,6 +105,18 @@ class CacheManager:
         self.length = {}                          # request id -> tokens in the cache
 
     # ---- device storage ----
+    def bytes_needed(self, element_size):
+        """Bytes that allocate() takes on the device: the page arenas (elements of element_size bytes) and the
+        per-request state rows."""
+        import math
+        total = 0
+        for g in self.groups:
+            total += len(g.layers) * g.pool.n_pages * 2 * g.need.kv_heads * self.page_size * g.need.head_dim * element_size
+        widths = {"float32": 4, "bfloat16": 2, "float16": 2, "int32": 4, "int64": 8, "float64": 8}
+        for need in self.state_needs.values():
+            total += self.max_requests * math.prod(need.shape) * widths.get(need.dtype, 4)
+        return total
+
     def allocate(self, device, dtype):
         import torch
         for g in self.groups:

@@ -78,7 +78,9 @@ class Engine:
         if kv_tokens is None:
             kv_tokens = max_requests * self.max_context
         kv_tokens = (kv_tokens + page_size - 1) // page_size * page_size
+        self.kv_tokens = kv_tokens
         self.cache = CacheManager(cache_needs(self.spec), kv_tokens, page_size, max_requests, self.max_context)
+        self._admit_memory()
         self.cache.allocate(self.device, self.dtype)
         self._caches = [self.cache.layer_view(i) if e.cache_of is None else self.cache.layer_view(e.cache_of, writable=False)
                         for i, e in enumerate(self.spec.run_order)]
@@ -98,6 +100,26 @@ class Engine:
         self._turn = 0
         self.steps = 0
         self.tokens_run = 0
+
+    HEADROOM_BYTES = 512 << 20
+
+    def _admit_memory(self):
+        """Weights are on the device already; the cache, the activations of the largest step and 512 MiB of
+        headroom must fit into what is free now, else MemoryError before anything more is allocated
+        (damendaemon/qwen2.py:551-553: weights + cache + workspace + 512 MiB against free memory)."""
+        element = 2 if self.dtype == torch.bfloat16 else 4
+        cache_bytes = self.cache.bytes_needed(element)
+        widest = max((getattr(l.feed_forward, "inner", 0) for l in self.spec.layers), default=0)
+        per_token = 4 * self.spec.width * 4 + (3 * self.spec.width + widest) * element
+        workspace = min(self.max_context * self.cache.max_requests, 8192) * per_token + self.cache.max_requests * self.spec.vocab_size * 4
+        free, total = torch.cuda.mem_get_info(self.device)
+        need = cache_bytes + workspace + self.HEADROOM_BYTES
+        if need > free:
+            gib = lambda b: f"{b / 2 ** 30:.2f} GiB"
+            raise MemoryError(f"the cache needs {gib(cache_bytes)} ({self.kv_tokens} tokens), a step's activations about "
+                              f"{gib(workspace)}, plus {gib(self.HEADROOM_BYTES)} of headroom: {gib(need)} in all, but only "
+                              f"{gib(free)} of {gib(total)} are free beside {gib(self.weight_bytes)} of weights; "
+                              f"ask for fewer cache tokens (kv_tokens / --kv-cache-tokens)")
 
     # ------------------------------------------------------------------ requests
     def live_requests(self):

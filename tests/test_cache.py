@@ -79,6 +79,12 @@ def test_groups_by_need_and_block_tables():
     m.check()
 
 
+def test_bytes_needed_counts_every_group_and_the_state_rows():
+    m = manager(window=24)        # 256 tokens: two layers of all keys, one windowed layer, 2 heads x 16, state 3 x 5 per request
+    assert m.bytes_needed(2) == 3 * 256 * 2 * 2 * 16 * 2 + 4 * 15 * 4
+    assert manager().bytes_needed(4) == 2 * 256 * 2 * 2 * 16 * 4
+
+
 def test_extend_is_all_or_nothing():
     m = manager(kv_tokens=64)
     m.admit("a"), m.admit("b")

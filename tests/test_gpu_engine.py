@@ -148,6 +148,22 @@ def test_step_validation_changes_nothing(models):
     assert tuple(none.shape) == (0, 512)
 
 
+def test_cache_that_does_not_fit_is_refused(models, monkeypatch):
+    """The cache, a step's activations and the headroom are held against the free memory before the cache is
+    allocated: a pool that cannot fit raises MemoryError and names what was asked for."""
+    from damendaemon_b200.engine import Engine
+    folder, config, requests, want = models["A", "float32"]
+    free_before = torch.cuda.mem_get_info(0)[0]
+    monkeypatch.setattr(Engine, "HEADROOM_BYTES", 1 << 50)
+    with pytest.raises(MemoryError, match="kv_tokens"):
+        Engine(folder, dtype="float32", kv_tokens=64, page_size=16, max_requests=4, device="cuda:0")
+    monkeypatch.undo()
+    torch.cuda.empty_cache()
+    assert torch.cuda.mem_get_info(0)[0] >= free_before - (64 << 20)
+    engine = Engine(folder, dtype="float32", kv_tokens=64, page_size=16, max_requests=4, device="cuda:0")
+    assert engine.cache.bytes_needed(4) == 64 * 2 * 2 * 64 * 4          # tokens x layers x (K, V) x width x 4 bytes
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(models, dtype, tmp_path):
     """The replay program itself, as a user runs it: mixed trace, few pages."""
