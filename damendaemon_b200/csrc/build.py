@@ -31,7 +31,7 @@ HERE = Path(__file__).resolve().parent
 LIBRARIES = {
     "core": ["errors.cu", "embed.cu", "layernorm.cu", "gemm_simt.cu", "kv_store.cu", "attention_rows.cu",
              "sampling.cu"],
-    "tensor": ["errors.cu", "gemm_tcgen05.cu", "attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu",
+    "tensor": ["errors.cu", "gemm_tcgen05.cu", "attention_decode.cu", "attention_decode_pages.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu",
                "mlp_decode.cu"],
 }
 HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]

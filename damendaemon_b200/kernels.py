@@ -46,6 +46,10 @@ _SIGNATURES = {
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
         "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                         + [_c_int] * 6 + [_c_float, _c_void, _c_void],
+        "dd_attention_decode_pages_supported": [_c_int] * 5,
+        "dd_attention_decode_pages_splits": [_c_int] * 5,
+        "dd_attention_decode_pages": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
+                                      _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
         "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
                                 _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 8
@@ -332,11 +336,24 @@ def attention_decode_supported(n_heads, kv_heads, head_dim, dtype):
     return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_decode_supported(n_heads, kv_heads, head_dim, BF16))
 
 
+def attention_decode_pages_supported(n_heads, kv_heads, head_dim, page_size, dtype):
+    return dtype == torch.bfloat16 and bool(
+        library("tensor").dd_attention_decode_pages_supported(n_heads, kv_heads, head_dim, page_size, BF16))
+
+
+def attention_decode_pages_splits(n_tokens, n_heads, page_size, context, device):
+    """The key split count the page-streaming decode kernel wants for this many tokens and this longest context."""
+    return int(library("tensor").dd_attention_decode_pages_splits(n_tokens, n_heads, page_size, context, sm_count(device)))
+
+
 def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
-                     k_new=None, v_new=None):
-    """Decode attention (one query per token) over a bfloat16 cache; see attention_decode_supported.
-    With k_new/v_new (row views of the buffer q lives in) the step's own keys and values are used
-    from there and written into the cache by this kernel; otherwise they must be in the cache already."""
+                     k_new=None, v_new=None, kernel="rows"):
+    """Decode attention (one query per token) over a bfloat16 cache. kernel 'rows': a warp copies key rows 16 bytes
+    at a time (see attention_decode_supported); 'pages': whole pages of a group of heads by TMA (see
+    attention_decode_pages_supported). With k_new/v_new (row views of the buffer q lives in) the step's own keys and
+    values are used from there and written into the cache by this kernel; otherwise they must be in the cache already."""
+    if kernel not in ("rows", "pages"):
+        raise KernelError(f"attention_decode: unknown kernel {kernel!r}")
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n = q.shape[0]
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
@@ -354,7 +371,8 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
         part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
         counters = _tile_counters(q.device, n * n_heads)
-    _call(library("tensor"), "dd_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(k_new, "k_new"), _ptr(v_new, "v_new"),
+    _call(library("tensor"), "dd_attention_decode" + ("_pages" if kernel == "pages" else ""), _ptr(q, "q"), q.stride(0),
+          _ptr(k_new, "k_new"), _ptr(v_new, "v_new"),
           _ptr(cache, "cache"), _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), _ptr(counters), n, n_heads, kv_heads, head_dim, page_size, n_pages,

@@ -191,6 +191,43 @@ def test_attention_decode_bf16(K, d, heads, page, n_splits, window):
     assert bool(same.all()), "the fused kernel did not write the new key and value into the cache"
 
 
+@pytest.mark.parametrize("heads,page", [(5, 16), (25, 16), (17, 32), (3, 64), (2, 128), (33, 16)])
+@pytest.mark.parametrize("n_splits", [1, 3, 11])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_pages(K, heads, page, n_splits, window):
+    """The page-streaming decode kernel (TMA boxes of a group of heads): contexts from 1 to 1000 keys that end anywhere
+    in a page, a far key, fragmented pages, a poisoned cache, head counts that fill one, two or three groups unevenly,
+    more splits than some requests have pages; then the fused cache write."""
+    K.library("tensor")
+    assert K.attention_decode_pages_supported(heads, heads, 64, page, torch.bfloat16)
+    assert not K.attention_decode_pages_supported(heads, heads, 128, page, torch.bfloat16)
+    assert not K.attention_decode_pages_supported(heads, heads, 64, 8, torch.bfloat16)
+    assert not K.attention_decode_pages_supported(heads, 1, 64, page, torch.bfloat16) or heads == 1
+    lengths = [300, 33, 1, 1000, 129, 512]
+    c = paged_case(K, torch.bfloat16, heads, heads, 64, page, lengths=lengths, new=[1] * 6,
+                   window=window, n_splits=n_splits, spike=5 if window is None else 250)
+    run = lambda q, cache, **kw: K.attention_decode(q, cache, c["ent"], c["pos"], c["table"], heads, c["scale"], window,
+                                                    n_splits=n_splits, kernel="pages", **kw)
+    out = run(c["q"], c["cache"])
+    again = run(c["q"], c["cache"])
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    assert torch.equal(out, again), "the split counters were not left at zero"
+    packed = c["packed"]
+    hd = heads * 64
+    wiped = c["cache"].clone()
+    for e, L in enumerate(lengths):
+        pg = int(c["table"][e, (L - 1) // page])
+        wiped[pg, :, :, (L - 1) % page] = float("nan")
+    fused = run(packed[:, :hd], wiped, k_new=packed[:, hd:2 * hd], v_new=packed[:, 2 * hd:])
+    assert K.read_error_flag(DEV) == 0
+    assert torch.equal(fused, out)
+    same = (wiped == c["cache"]) | (torch.isnan(wiped.float()) & torch.isnan(c["cache"].float()))
+    assert bool(same.all()), "the fused kernel did not write the new key and value into the cache"
+    assert 1 <= K.attention_decode_pages_splits(8, heads, page, 1000, DEV) <= (1000 + page - 1) // page
+
+
 @pytest.mark.parametrize("d,heads,kv_heads,page", [(64, 5, 5, 16), (128, 4, 2, 8), (64, 6, 1, 32)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attention_prefill_bf16(K, d, heads, kv_heads, page, window):
