@@ -989,8 +989,10 @@ DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = 
 DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_tile, int* cluster) {
     // Up to 64 tokens the tile is 128 features x 16, 32 or 64 tokens. Above, it is 128 tokens x 128, 192 or 256
     // features (the value returned in *token_tile is then the feature width).
+    const int kblocks = dd_ceil_div(K, BK);
+    const bool long_k = kblocks > 32;                 // more than 2,048: worth splitting even for 17 to 64 tokens
     int bn = 128;
-    if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = 64;
+    if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = long_k ? 64 : 32;
     else {
         // Tiles of 128 tokens x c features on one SM, or of 256 tokens x c features on a pair of SMs (less L2
         // traffic per flop). A round of one tile per SM was measured to take about as long as c + 64 columns
@@ -1015,13 +1017,13 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     if (token_tile) *token_tile = bn;
     if (cluster) *cluster = 0;
     const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
-    const int kblocks = dd_ceil_div(K, BK);
     // A step of a few tokens has a few dozen tiles at most: split K inside clusters so that about as many
     // blocks as there are SMs stream the weights, all in one wave (a cluster must be resident as a whole).
-    // Above 32 tokens the reduction of a wide tile costs more than the split saves unless the tiles are very few
-    // (measured at 64 tokens: 4800 and 6400 features faster unsplit, 1600 features faster split).
+    // From 17 tokens on the reduction of the wider tiles costs more than the split saves unless K is long: measured
+    // at 64 tokens and K = 1600, 1600 features take 13.4 us split eightfold and 7.3 us unsplit in tiles of 32 tokens
+    // (6400 features: 9.9 against 8.8 us); with K = 6400 the eightfold split stays ahead (12.5 against 18.8 us).
     int splits = 1;
-    if (M <= 64 && tiles * 2 <= sm_count && (M <= 32 || tiles <= 16)) {
+    if (M <= 64 && tiles * 2 <= sm_count && (M <= 16 || (long_k && (M <= 32 || tiles <= 16)))) {
         splits = sm_count / tiles;       // fewer, so that two kernels' blocks could sit side by side, measured slower
         if (splits > 8) splits = 8;
         if (splits > kblocks / 2) splits = kblocks / 2;
