@@ -46,15 +46,17 @@ def _cache_case(batch, context, dev, copies):
     return caches, table
 
 
-def _decode_case(batch, context, dev):
+def _decode_case(batch, context, dev, kernel="pages"):
     copies = max(2, min(12, (300 << 20) // (batch * context * H * D * 4)))
     caches, table = _cache_case(batch, context, dev, copies)
     ent = torch.arange(batch, dtype=torch.int32, device=dev)
     pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
     q = torch.randn(batch, H * D, device=dev).to(torch.bfloat16)
-    want = -(-(K.sm_count(dev) * 4) // (batch * H))
-    splits = max(1, min(want, (context + 127) // 128, 32))
-    run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, None, n_splits=splits)
+    if kernel == "pages":
+        splits = K.attention_decode_pages_splits(batch, H, PAGE, context, dev)
+    else:
+        splits = max(1, min(-(-(K.sm_count(dev) * 2) // (batch * H)), (context + 127) // 128, 32))
+    run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, None, n_splits=splits, kernel=kernel)
     return run, {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
 
 
@@ -68,12 +70,14 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05"):
 
 
 def build(name, device="cuda:0"):
-    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> | attn_prefill | attn_prefill_mma |
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> (page streaming) | attn_decode_rows_b<batch> | attn_prefill | attn_prefill_mma |
     attn_prefill_long (one prompt of 4,096 tokens)"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
         return _gemm_case(parts[1], int(parts[2][1:]), device)
+    if name.startswith("attn_decode_rows_b"):
+        return _decode_case(int(name[len("attn_decode_rows_b"):]), 768, device, kernel="rows")
     if name.startswith("attn_decode_b"):
         return _decode_case(int(name[len("attn_decode_b"):]), 768, device)
     if name == "attn_prefill":
