@@ -79,9 +79,9 @@ __device__ __forceinline__ float activation_for(float u, int act, int out_dtype)
 
 // The cluster variant keeps a reduce buffer of (BM + 8) x BN floats beside the stages.
 template <int BN> struct ClusterConfig {
-    // deep rings: with 5 stages (two blocks per SM, so that the next kernel's blocks could prefetch beside this
-    // kernel's) every size measured 15-40% slower than with one block per SM and 8 stages
-    static constexpr int STAGES = BN >= 64 ? 6 : 8;
+    // 16 tokens: 5 stages, so that two blocks fit on an SM, with enough splits that a block seldom reuses a stage
+    // (with the splits of the 8-stage rings, 5 stages measured 15-40% slower; with more splits, 5-20% faster)
+    static constexpr int STAGES = BN >= 64 ? 6 : (BN == 16 ? 5 : 8);
     static constexpr int STAGE_BYTES = Config<BN>::STAGE_BYTES;
     static constexpr int A_BYTES = Config<BN>::A_BYTES;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -1024,7 +1024,10 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     // (6400 features: 9.9 against 8.8 us); with K = 6400 the eightfold split stays ahead (12.5 against 18.8 us).
     int splits = 1;
     if (M <= 64 && tiles * 2 <= sm_count && (M <= 16 || (long_k && (M <= 32 || tiles <= 16)))) {
-        splits = sm_count / tiles;       // fewer, so that two kernels' blocks could sit side by side, measured slower
+        // Up to 16 tokens the rings are 5 stages deep, so two blocks fit on an SM and the next GEMM's blocks can ask for
+        // their weights beside this one's: about 1.35 blocks per SM measured best (4800 features: 5 or 6 splits 6.3 us,
+        // 3 splits 7.0; 6400 features: 4 splits 6.8, 2 splits 8.5; more than two blocks per SM: 10.7 and more).
+        splits = bn == 16 ? (sm_count * 27 / 20 + tiles / 2) / tiles : sm_count / tiles;
         if (splits > 8) splits = 8;
         if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
