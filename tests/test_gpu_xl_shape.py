@@ -49,3 +49,37 @@ def test_xl_layer_sizes(xl, dtype):
             assert int(got[r].argmax()) == int(want[i].argmax())
     engine.finish("r")
     assert engine.cache.used_tokens == 0
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_xl_decode_of_eight_requests(xl, use_graph):
+    """Eight requests of different lengths decoded together, in bfloat16: 8 x 25 heads is where the engine switches to
+    the decode attention kernel that streams whole cache pages, with and without CUDA graphs. Every decoded position of
+    every request is held against the plain implementation run on that request alone."""
+    from damendaemon_b200.engine import Engine, StepEntry
+    folder = xl[0]
+    plain = PlainGpt2(folder)
+    g = torch.Generator().manual_seed(11)
+    lengths, n_decode = [5, 17, 33, 64, 100, 130, 16, 250], 6
+    tokens = [torch.randint(0, 50257, (n + n_decode,), generator=g).tolist() for n in lengths]
+    want, moved = [], 0.0
+    for n, seq in zip(lengths, tokens):
+        rows = list(range(n - 1, n + n_decode))
+        exact = plain.logits(seq, rows=rows).float()
+        moved = max(moved, (plain.logits(seq, rounded=torch.bfloat16, rows=rows).float() - exact).abs().max().item())
+        want.append(exact)
+    engine = Engine(folder, dtype="bfloat16", kv_tokens=1024, page_size=16, max_requests=8, use_graph=use_graph)
+    for group in engine.cache.groups:
+        group.arena.fill_(float("nan"))
+    tol = 3.0 * moved + 2e-3
+    out = engine.step([StepEntry(r, tokens[r][:n], [n - 1]) for r, n in enumerate(lengths)]).cpu()
+    for r in range(8):
+        assert (out[r] - want[r][0]).abs().max().item() < tol, f"prompt of request {r}"
+    for step in range(n_decode):
+        out = engine.step([StepEntry(r, [tokens[r][n + step]], [0]) for r, n in enumerate(lengths)]).cpu()
+        for r in range(8):
+            err = (out[r] - want[r][1 + step]).abs().max().item()
+            assert err < tol, f"request {r}, decoded token {step}: differs by {err:.3e} (allowed {tol:.3e})"
+    for r in range(8):
+        engine.finish(r)
+    assert engine.cache.used_tokens == 0
