@@ -835,17 +835,33 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         const int tid = threadIdx.x - 64;                 // 0..127
         const int first_feature = rank * slice;
         const int my_features = max(0, min(slice, BM - first_feature));
-        for (int idx = tid; idx < my_features * BN; idx += 128) {
-            const int lf = idx % my_features, tok = idx / my_features;     // neighbouring threads, neighbouring features
-            const int n = n0 + first_feature + lf, m = m0 + tok;
-            if (n >= p.N || m >= p.M) continue;
-            float v = 0.f;
-            for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
-            if (p.bias) v += p.bias[n];
-            v = activation_for(v, p.act, p.out_dtype);
-            if (p.residual) v += p.residual[(size_t)m * p.ldr + n];
-            if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+        // Eight outputs of a thread at a time: their residual values (the output itself, as a rule, so no load may be
+        // moved across a store by the compiler) are all requested before the first result is written; one after the
+        // other, each cost a trip to L2.
+        const int total = my_features * BN;
+        for (int base = tid; base < total; base += 128 * 8) {
+            float res[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * 128;
+                const int lf = idx % my_features, tok = idx / my_features;   // neighbouring threads, neighbouring features
+                const int n = n0 + first_feature + lf, m = m0 + tok;
+                res[u] = (p.residual && idx < total && n < p.N && m < p.M) ? p.residual[(size_t)m * p.ldr + n] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * 128;
+                if (idx >= total) break;
+                const int lf = idx % my_features, tok = idx / my_features;
+                const int n = n0 + first_feature + lf, m = m0 + tok;
+                if (n >= p.N || m >= p.M) continue;
+                float v = 0.f;
+                for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
+                if (p.bias) v += p.bias[n];
+                v = activation_for(v, p.act, p.out_dtype) + res[u];
+                if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+            }
         }
     }
     tc::fence_before_sync();
