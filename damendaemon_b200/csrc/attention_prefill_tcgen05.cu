@@ -3,15 +3,17 @@
 // A block owns 128 consecutive query tokens of one request and one head and walks the request's keys in blocks
 // of 128 straight out of the cache pages. Three roles:
 //   warp 0      TMA: the query tile once, then per key block one box per cache page for the keys and one for
-//               the values (each lane issues the boxes of one page), several blocks ahead;
+//               the values (each lane issues one box), several blocks ahead;
 //   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, accumulator in TMEM, two buffers so that the
 //               scores of block j+2 are computed while the softmax works on j and j+1), then O_j = P_j V_j
 //               (128 x 64) from the probabilities that the softmax warps left in shared memory; V is read as it
 //               lies in the cache, as an MN-major operand;
-//   warps 2..5  softmax: a thread owns one query row (its TMEM lane), so the running maximum and sum need no
-//               shuffles; it takes the 128 scores of a block into registers with four TMEM loads in flight,
-//               writes P as bfloat16 in the swizzled K-major layout the MMA reads, and keeps the output
-//               row in registers: O = (O + P_{j-1} V_{j-1}) * exp2(m_{j-1} - m_j), float32 throughout.
+//   warps 2..9  softmax: two threads own one query row (its TMEM lane), one for each half of a block's 128 keys,
+//               so only the two halves' maxima are exchanged (shared memory, one barrier per block) and nothing is
+//               shuffled; a thread takes its 64 scores into registers with two TMEM loads in flight, writes P as
+//               bfloat16 in the swizzled K-major layout the MMA reads, and keeps half of the output row in
+//               registers: O = (O + P_{j-1} V_{j-1}) * exp2(m_{j-1} - m_j), float32 throughout. With one thread per
+//               row (four warps) a block cost the softmax 1.3 us against 0.3 us of MMAs.
 // Scores, softmax and the weighted sum of values are float32 (damendaemon/kernels.py:147-178 for the mask and
 // the stable softmax; damendaemon/qwen2.py:754-770 for the offset-aware causal rule). Keys outside the live
 // range (beyond the last query of the tile, before the window, pages that were given back) are never multiplied
@@ -23,11 +25,12 @@
 #include <math_constants.h>
 
 namespace {
-constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 192, STAGES = 4;
+constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 64 + 256, STAGES = 4;
 constexpr int TILE_BYTES = BKV * D * 2;             // one 128 x 64 bf16 tile: 16 KB
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // keys, then values
 constexpr int P_BYTES = 2 * TILE_BYTES;             // 128 x 128 probabilities as two 64-key halves
-constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024 + 256;
+constexpr int EXCHANGE_BYTES = 6 * BQ * 4;           // row maxima of the two halves (two buffers), then the two row sums
+constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024 + 256 + EXCHANGE_BYTES;
 constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O_j: 2 x 64 columns
 constexpr int S_COL = 0, O_COL = 256;
 
@@ -39,6 +42,7 @@ struct AttnParams {
     int* error_flag;
     int n_entries, max_blocks, out_stride, H, KH, P, n_pages, window;
     float scale_log2e;
+    int new_rows;                   // 1: this step's keys and values are also at hand as rows beside the queries
     unsigned long long* timeline;   // null, or 64 time stamps (ns) per block: where a block's time goes
 };
 
@@ -56,6 +60,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 const __grid_constant__ CUtensorMap map_k_new, const __grid_constant__ CUtensorMap map_v_new,
                                  const AttnParams p) {
     // which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once.
     int e = 0, tile = blockIdx.x, len = 0;
@@ -79,6 +84,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     uint64_t* o_full = p_ready + 2;       // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* softmax_abort = abort_flag + 1;          // written by softmax threads only, read after their barrier
+    float* row_max = reinterpret_cast<float*>(sP + 2 * P_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, kh = h / (p.H / p.KH);
@@ -98,10 +105,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         tc::mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) {
             tc::mbar_init(&s_full[b], 1);
-            tc::mbar_init(&p_ready[b], 4);        // one arrival per softmax warp
+            tc::mbar_init(&p_ready[b], 8);        // one arrival per softmax warp
             tc::mbar_init(&o_full[b], 1);
         }
         *abort_flag = 0;
+        *softmax_abort = 0;
         tc::fence_barrier_init();
         tc::fence_proxy_async();
     }
@@ -147,38 +155,53 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int kb = kb_first + j * BKV;
             uint8_t* k_dst = sKV + s * STAGE_BYTES;
             uint8_t* v_dst = k_dst + TILE_BYTES;
+            if (p.new_rows && kb >= pos_first - q0) {
+                // Every key of this block is one of this step's own: they lie row after row beside the queries, so one
+                // box of 128 rows brings the keys and one the values (a box per cache page costs the TMA unit about
+                // 60 ns each, 1 us per block with pages of 16 tokens, which is what bounded whole prompts). Rows past
+                // the entry are other requests' tokens or zeros: masked by position like any key after the query.
+                if (lane == 0) {
+                    const int row = (row0 - q0) + kb - (pos_first - q0);       // the entry's first row + (key - its first position)
+                    tc::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                    tc::tma_load_2d(k_dst, &map_k_new, kh * D, row, &kv_full[s]);
+                    tc::tma_load_2d(v_dst, &map_v_new, kh * D, row, &kv_full[s]);
+                    if (stamps && j < 8) stamps[56 + j] = tc::global_ns();
+                }
+                continue;
+            }
             const int first_entry = kb / p.P;
             if (first_entry / 32 != window_at) {
                 window_at = first_entry / 32;
                 held = ahead;
                 ahead = table_window(window_at + 1);
             }
-            const int page = __shfl_sync(0xffffffffu, held, (first_entry + lane) & 31);
+            // lanes 0 .. pages-1 fetch the key boxes of the block's pages, the next `pages` lanes the value boxes
+            const int slot = lane < pages_per_block ? lane : lane - pages_per_block;
+            const bool values = lane >= pages_per_block;
+            const int page = __shfl_sync(0xffffffffu, held, (first_entry + slot) & 31);
             bool valid = false;
-            if (lane < pages_per_block) {
-                const int key0 = kb + lane * p.P;
+            if (lane < 2 * pages_per_block) {
+                const int key0 = kb + slot * p.P;
                 valid = key0 <= pos_last && key0 + p.P > kv_lo;
                 if (valid && (page < 0 || page >= p.n_pages)) {
                     atomicOr(p.error_flag, 4);
                     valid = false;
                 }
             }
-            const int n_valid = __popc(__ballot_sync(0xffffffffu, valid));
-            if (lane < pages_per_block) {
+            const int n_valid = __popc(__ballot_sync(0xffffffffu, valid));          // boxes, keys and values counted apart
+            if (lane < 2 * pages_per_block) {
                 if (valid) {
-                    const int k_row = ((page * 2 + 0) * p.KH + kh) * p.P;
-                    const int v_row = ((page * 2 + 1) * p.KH + kh) * p.P;
-                    tc::tma_load_2d(k_dst + lane * page_bytes, &map_kv, 0, k_row, &kv_full[s]);
-                    tc::tma_load_2d(v_dst + lane * page_bytes, &map_kv, 0, v_row, &kv_full[s]);
-                } else {
+                    const int row = ((page * 2 + (values ? 1 : 0)) * p.KH + kh) * p.P;
+                    tc::tma_load_2d((values ? v_dst : k_dst) + slot * page_bytes, &map_kv, 0, row, &kv_full[s]);
+                } else if (values) {
                     // no live key in this page: its scores are all masked; its value rows must be zeros
-                    uint4* z = reinterpret_cast<uint4*>(v_dst + lane * page_bytes);
+                    uint4* z = reinterpret_cast<uint4*>(v_dst + slot * page_bytes);
                     for (uint32_t i = 0; i < page_bytes / 16; ++i) z[i] = make_uint4(0, 0, 0, 0);
                     tc::fence_proxy_async();
                 }
             }
             __syncwarp();
-            if (lane == 0) tc::mbar_expect_tx(&kv_full[s], (uint32_t)n_valid * 2 * page_bytes);
+            if (lane == 0) tc::mbar_expect_tx(&kv_full[s], (uint32_t)n_valid * page_bytes);
             if (stamps && lane == 0 && j < 8) stamps[56 + j] = tc::global_ns();
         }
     } else if (warp == 1) {
@@ -221,50 +244,58 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         }
     } else {
-        // ---- softmax and output: thread = query row = TMEM lane ----
-        const int quarter = warp & 3;
+        // ---- softmax and output: two threads per query row (its TMEM lane), one for each half of a block's keys ----
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int qpos = pos_first + r;
         const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float o[D];
+        constexpr int HALF = BKV / 2, DH = D / 2;          // keys and output dimensions of one thread
+        float o[DH];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
-        float m = -CUDART_INF_F, l = 0.f;
-        bool ok = true;
+        for (int i = 0; i < DH; ++i) o[i] = 0.f;
+        float m = -CUDART_INF_F, l = 0.f;                  // m is the row's, l this thread's half of the sum
         for (int j = 0; j < n_blocks; ++j) {
-            const int b = j & 1, kb = kb_first + j * BKV;
-            if (!tc::mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            const int b = j & 1, kb = kb_first + j * BKV, k0 = kb + half * HALF;
+            const bool have = tc::mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag);
+            if (!have) *softmax_abort = 1;
             tc::fence_after_sync();
             const bool stamp = stamps && threadIdx.x == 64 && j < 8;
             if (stamp) stamps[8 + 4 * j] = tc::global_ns();
-            const uint32_t s_addr = lane_addr + S_COL + b * BKV;
-            const bool need_mask = kb + BKV - 1 > qpos || kb < qlo;
-            // the whole row of this block's scores: four loads in flight, one wait
-            uint32_t sv[BKV];
-#pragma unroll
-            for (int c0 = 0; c0 < BKV; c0 += 32) tc::tmem_ld_x32(s_addr + c0, sv + c0);
-            tc::tmem_ld_wait();
-            if (need_mask) {
-#pragma unroll
-                for (int i = 0; i < BKV; ++i)
-                    if (kb + i > qpos || kb + i < qlo) sv[i] = 0xff800000u;      // -inf: replaced, whatever was there
-            }
+            const uint32_t s_addr = lane_addr + S_COL + b * BKV + half * HALF;
+            // this thread's 64 scores of the block: two loads in flight, one wait
+            uint32_t sv[HALF];
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (have) {
 #pragma unroll
-            for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                for (int c0 = 0; c0 < HALF; c0 += 32) tc::tmem_ld_x32(s_addr + c0, sv + c0);
+                tc::tmem_ld_wait();
+                if (k0 + HALF - 1 > qpos || k0 < qlo) {
+#pragma unroll
+                    for (int i = 0; i < HALF; ++i)
+                        if (k0 + i > qpos || k0 + i < qlo) sv[i] = 0xff800000u;      // -inf: replaced, whatever was there
+                }
+#pragma unroll
+                for (int i = 0; i < HALF; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            }
+            // the two halves of a row exchange their maxima (buffers alternate, so one barrier per block is enough)
+            float* xchg = row_max + (j & 1) * 2 * BQ;
+            xchg[half * BQ + r] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (*softmax_abort) break;                     // the same decision in all eight warps
+            const float mx = fmaxf(xchg[r], xchg[BQ + r]);
             if (stamp) stamps[9 + 4 * j] = tc::global_ns();
             const float m_new = fmaxf(m, mx * p.scale_log2e);      // the scale is positive
             const float alpha = m_new == -CUDART_INF_F ? 1.f : exp2_approx(m - m_new);
             const float msub = m_new == -CUDART_INF_F ? 0.f : m_new;
             m = m_new;
             // exponentials (a masked score gives exactly 0), their sum, P as bfloat16 into shared memory (K-major,
-            // 128-byte swizzle: 16-byte chunk c of row r lies at chunk c ^ (r & 7))
+            // 128-byte swizzle: 16-byte chunk c of row r lies at chunk c ^ (r & 7)); this thread's keys are one
+            // 128-byte row of the block's half `half`
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint8_t* p_row = sP + b * P_BYTES + r * 128;
+            uint8_t* p_row = sP + b * P_BYTES + half * TILE_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < BKV / 8; ++c) {
+            for (int c = 0; c < HALF / 8; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -273,15 +304,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     sum4[i] += p0 + p1;
                     w[i] = pack_bf16(p0, p1);
                 }
-                *reinterpret_cast<uint4*>(p_row + (c / 8) * TILE_BYTES + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l = l * alpha + sum;
+            l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (kb + BKV - 1 > pos_last) {
                 // value rows of keys past the tile's last query: unwritten cache slots, to be zeros under P = 0
                 const int s = j % STAGES;
-                if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) { ok = false; break; }
-                if (kb + r > pos_last) {
+                if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) *softmax_abort = 1;
+                else if (half == 0 && kb + r > pos_last) {
                     uint4* z = reinterpret_cast<uint4*>(sKV + s * STAGE_BYTES + TILE_BYTES + r * 128);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) z[i] = make_uint4(0, 0, 0, 0);
@@ -293,42 +323,43 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (lane == 0) tc::mbar_arrive(&p_ready[b]);
             if (stamp) stamps[10 + 4 * j] = tc::global_ns();
             if (j > 0) {
-                // O = (O + P_{j-1} V_{j-1}) * alpha_j
+                // O = (O + P_{j-1} V_{j-1}) * alpha_j, this thread's 32 output dimensions
                 const int pb = (j - 1) & 1;
-                if (!tc::mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                tc::fence_after_sync();
-                uint32_t v[32];
-#pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + c0, v);
+                if (!tc::mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, abort_flag)) *softmax_abort = 1;
+                else {
+                    tc::fence_after_sync();
+                    uint32_t v[DH];
+                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + half * DH, v);
                     tc::tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + __uint_as_float(v[i])) * alpha;
+                    for (int i = 0; i < DH; ++i) o[i] = (o[i] + __uint_as_float(v[i])) * alpha;
                 }
             }
             if (stamp) stamps[11 + 4 * j] = tc::global_ns();
         }
-        if (ok) {
+        // the last block's P.V, the two halves of the row sum, and the output row
+        {
             const int pb = (n_blocks - 1) & 1;
-            ok = tc::mbar_wait(&o_full[pb], ((n_blocks - 1) >> 1) & 1, abort_flag);
-            if (ok) {
+            if (!*softmax_abort && !tc::mbar_wait(&o_full[pb], ((n_blocks - 1) >> 1) & 1, abort_flag)) *softmax_abort = 1;
+            row_max[4 * BQ + half * BQ + r] = l;
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (!*softmax_abort) {
                 tc::fence_after_sync();
-                uint32_t v[32];
-#pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + c0, v);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
-                }
+                uint32_t v[DH];
+                tc::tmem_ld_x32(lane_addr + O_COL + pb * D + half * DH, v);
+                tc::tmem_ld_wait();
                 if (r < rows) {
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
-                    __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * D;
+                    const float sum = row_max[4 * BQ + r] + row_max[5 * BQ + r];
+                    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+                    __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * D + half * DH;
 #pragma unroll
-                    for (int c = 0; c < D; c += 8)
-                        *reinterpret_cast<uint4*>(dst + c) =
-                            make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
-                                       pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
+                    for (int c = 0; c < DH; c += 8) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = (o[c + i] + __uint_as_float(v[c + i])) * inv;
+                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
+                                                                          pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                    }
                 }
             }
         }
@@ -388,8 +419,10 @@ DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, i
 
 // The arguments of dd_attention_prefill: entries are runs of consecutive tokens of one request; entry e holds
 // flattened tokens entry_start[e] .. entry_start[e+1]-1 at positions entry_pos0[e] ...; block_table row e is its
-// pages. cache [n_pages, 2, n_kv_heads, page_size, 64] bf16.
-DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* cache, const int* entry_start,
+// pages. cache [n_pages, 2, n_kv_heads, page_size, 64] bf16, which must hold this step's keys and values already.
+// k_new/v_new: null, or this step's keys and values as rows of q_stride bf16 (kv head g at g*64), the same values
+// the cache holds: key blocks that lie wholly in this step are then read from there, one TMA box per block.
+DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, const void* cache, const int* entry_start,
                                         const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
                                         int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
                                         int head_dim, int page_size, int n_pages, int window, float scale,
@@ -409,8 +442,14 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
         if (e != cudaSuccess) return dd_fail("dd_attention_prefill_tcgen05: shared memory of %d bytes refused: %s", SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    CUtensorMap map_q, map_kv;
+    if ((k_new == nullptr) != (v_new == nullptr) || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15))
+        return dd_fail("dd_attention_prefill_tcgen05: k_new and v_new come together, 16-byte aligned");
+    CUtensorMap map_q, map_kv, map_k_new, map_v_new;
     if (int e = make_map(&map_q, q, (unsigned long long)n_tokens, n_heads * D, q_stride, BQ, "the queries")) return e;
+    // this step's keys and values as rows of the same stride as the queries (the fused projection's output), or the
+    // queries again as a stand-in that is never read
+    if (int e = make_map(&map_k_new, k_new ? k_new : q, (unsigned long long)n_tokens, (k_new ? n_kv_heads : n_heads) * D, q_stride, BKV, "this step's keys")) return e;
+    if (int e = make_map(&map_v_new, v_new ? v_new : q, (unsigned long long)n_tokens, (v_new ? n_kv_heads : n_heads) * D, q_stride, BKV, "this step's values")) return e;
     const unsigned long long kv_rows = (unsigned long long)n_pages * 2 * n_kv_heads * page_size;
     if (int e = make_map(&map_kv, cache, kv_rows, D, D, page_size, "the cache")) return e;
     AttnParams p;
@@ -419,8 +458,9 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.n_entries = n_entries; p.max_blocks = max_blocks; p.out_stride = out_stride; p.H = n_heads; p.KH = n_kv_heads;
     p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
     p.timeline = g_timeline;
+    p.new_rows = k_new != nullptr;
     // an upper bound of the number of 128-row tiles; blocks beyond the real count return at once
     dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, n_heads);
-    dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, p);
+    dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, map_k_new, map_v_new, p);
     return dd_check_launch("dd_attention_prefill_tcgen05");
 }

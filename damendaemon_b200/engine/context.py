@@ -64,7 +64,8 @@ class StepContext:
             if self.runtime.attention != "mma" and \
                     kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype):
                 return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window,
-                                                 kernel="tcgen05")
+                                                 kernel="tcgen05", k_new=k if cache.writable else None,
+                                                 v_new=v if cache.writable else None)
             if kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
                 return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,

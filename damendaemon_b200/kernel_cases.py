@@ -64,8 +64,10 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05"):
     caches, table = _cache_case(prompts, length, dev, 4)
     start = torch.arange(prompts + 1, dtype=torch.int32, device=dev) * length
     pos0 = torch.zeros(prompts, dtype=torch.int32, device=dev)
-    q = torch.randn(prompts * length, H * D, device=dev).to(torch.bfloat16)
-    run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None, kernel=kernel)
+    qkv = torch.randn(prompts * length, 3 * H * D, device=dev).to(torch.bfloat16)      # as the fused projection leaves them
+    q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
+    new = {"k_new": k, "v_new": v} if kernel == "tcgen05" else {}
+    run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None, kernel=kernel, **new)
     return run, {"bytes": prompts * length * H * D * 6, "flops": prompts * 4 * (length * (length + 1) // 2) * H * D}
 
 

@@ -275,6 +275,14 @@ def test_attention_prefill_tcgen05(K, heads, kv_heads, page, window):
     assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
     rows = K.attention_rows(c["q"], c["cache"], c["ent"], c["pos"], c["table"], heads, c["scale"], window)
     assert (out.float() - rows.float()).abs().max() < tol(torch.bfloat16)
+    # with this step's keys and values at hand as rows beside the queries, whole key blocks of the step are read from
+    # there instead of page by page: the same values, so the same result bit for bit
+    hd, kd = heads * 64, kv_heads * 64
+    packed = c["packed"]
+    direct = K.attention_prefill(packed[:, :hd], c["cache"], entry_start, entry_pos0, c["table"], heads, c["scale"], window,
+                                 kernel="tcgen05", k_new=packed[:, hd:hd + kd], v_new=packed[:, hd + kd:])
+    assert K.read_error_flag(DEV) == 0
+    assert torch.equal(direct, out)
 
 
 def test_attention_rejects_bad_sizes(K):
