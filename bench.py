@@ -90,8 +90,9 @@ def make_runtime(config, batch, use_graph=True, seed=0):
     arch = architecture_of(config)
     typed = arch.parse_config(config)
     tensors = arch.random_tensors(typed, seed, torch.bfloat16, device="cuda")
-    runtime = Runtime(None, config=config, tensors=tensors, dtype="bfloat16", max_batch=batch,
-                      kv_cache_tokens=batch * config["n_positions"], use_graph=use_graph, token_budget=4096)
+    slots = max(batch, 2)           # the prefill of two prompts runs on the same engine
+    runtime = Runtime(None, config=config, tensors=tensors, dtype="bfloat16", max_batch=slots,
+                      kv_cache_tokens=slots * config["n_positions"], use_graph=use_graph, token_budget=4096)
     del tensors
     torch.cuda.empty_cache()
     return runtime

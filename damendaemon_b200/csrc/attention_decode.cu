@@ -106,21 +106,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
     for (int blk = k0 / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
         asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + min(blk, max_blocks - 1)));
-    dd_grid_wait();
-    STAMP(1);
-
-    // the query as the A operand: row 0 of a 16-row tile, every other row zero
-    uint32_t qf[KS][4];
-    {
-        const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * D;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qf[ks][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * t4) : 0u;
-            qf[ks][1] = 0u;
-            qf[ks][2] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + 2 * t4) : 0u;
-            qf[ks][3] = 0u;
-        }
-    }
     const size_t head_plane = (size_t)P * D;
     const size_t page_stride = 2 * (size_t)H * head_plane;       // key/value heads = heads here
     const size_t k_off = (size_t)h * head_plane + c * 8;
@@ -185,8 +170,37 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     int pages[STAGES][STEPS];          // of the tiles about to be issued; the loop below is unrolled over its slots
 #pragma unroll
     for (int i = 0; i < STAGES; ++i) lookup(i, pages[i]);
+    // The first tiles are requested while the projection that produces the query is still running: the cache holds
+    // earlier steps' keys and values. Only the tile with the token's own position takes its row from k_new/v_new and
+    // has to wait, and with it every tile after it (copy groups complete in order).
+    int issued = 0;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
+        const bool early = issued == i && (k_new == nullptr || first_key + i * WARPS * TILE + TILE <= pos);
+        if (early) {
+            if (i < n_tiles) issue(i, pages[i]);
+            cp_commit();
+            issued = i + 1;
+        }
+    }
+    dd_grid_wait();
+    STAMP(1);
+
+    // the query as the A operand: row 0 of a 16-row tile, every other row zero
+    uint32_t qf[KS][4];
+    {
+        const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * t4) : 0u;
+            qf[ks][1] = 0u;
+            qf[ks][2] = g == 0 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + 2 * t4) : 0u;
+            qf[ks][3] = 0u;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (i < issued) continue;
         if (i < n_tiles) issue(i, pages[i]);
         cp_commit();
     }

@@ -44,11 +44,11 @@ class StepContext:
         kv, table = cache.kv, self.block_table(cache.group)
         kv_heads, head_dim = kv.shape[2], kv.shape[4]
         fast = self.runtime.attention != "rows"
-        if self.decode_only and fast and self.runtime.attention != "mma" and self.n_tokens * n_heads >= 100 and \
+        if self.decode_only and fast and self.runtime.attention != "mma" and self.n_tokens * n_heads >= 150 and \
                 kernels.attention_decode_pages_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype):
             # whole pages of a group of heads by TMA; it too takes the new keys and values from the projection. Measured
-            # with 25 heads and 768 keys: faster than the row kernel from 4 tokens on (11.0 against 11.8 us; 11.6 against
-            # 15.9 at 8 tokens; 54 against 69 at 64), slower below (9.8 against 8.0 us at two tokens), hence the threshold
+            # with 25 heads and 768 keys: faster than the row kernel from 8 tokens on (11.6 against 14.0 us; 54 against 68
+            # at 64), slower at 4 and below (11.0 against 9.8 us; 9.1 against 5.5 at one token), hence the threshold
             splits = kernels.attention_decode_pages_splits(self.n_tokens, n_heads, kv.shape[3], self.split_context, q.device)
             return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                             n_splits=splits, k_new=k if cache.writable else None,
