@@ -31,7 +31,7 @@ constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // keys, then values
 constexpr int P_BYTES = 2 * TILE_BYTES;             // 128 x 128 probabilities as two 64-key halves
 constexpr int EXCHANGE_BYTES = 6 * BQ * 4;           // row maxima of the two halves (two buffers), then the two row sums
 constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024 + 256 + EXCHANGE_BYTES;
-constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O_j: 2 x 64 columns
+constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O: 64 columns
 constexpr int S_COL = 0, O_COL = 256;
 
 struct AttnParams {
@@ -81,7 +81,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     uint64_t* q_full = kv_empty + STAGES;
     uint64_t* s_full = q_full + 1;        // [2]
     uint64_t* p_ready = s_full + 2;       // [2]
-    uint64_t* o_full = p_ready + 2;       // [2]
+    uint64_t* o_full = p_ready + 2;       // [0]: the P.V product of a block has been added to the output (one phase per block)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* softmax_abort = abort_flag + 1;          // written by softmax threads only, read after their barrier
@@ -232,12 +232,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (stamps && j < 8) stamps[40 + 2 * j] = tc::global_ns();
                 const uint32_t v_addr = tc::smem_u32(sKV + s * STAGE_BYTES + TILE_BYTES);
                 const uint32_t p_addr = tc::smem_u32(sP + b * P_BYTES);
-                const uint32_t tmem_o = tmem_base + O_COL + b * D;
+                const uint32_t tmem_o = tmem_base + O_COL;          // the output accumulates in TMEM over all blocks
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k)
                     tc::mma_bf16(tmem_o, tc::smem_desc_sw128(p_addr + (k / 4) * TILE_BYTES + (k % 4) * 32),
-                                 tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o, k > 0 ? 1u : 0u);
-                tc::mma_commit(&o_full[b]);
+                                 tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                tc::mma_commit(&o_full[0]);
                 tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
                 if (j + 2 < n_blocks) issue_scores(j + 2);   // its score buffer is free: P_j exists
                 if (stamps && j < 8) stamps[41 + 2 * j] = tc::global_ns();
@@ -251,10 +251,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int HALF = BKV / 2, DH = D / 2;          // keys and output dimensions of one thread
-        float o[DH];
-#pragma unroll
-        for (int i = 0; i < DH; ++i) o[i] = 0.f;
-        float m = -CUDART_INF_F, l = 0.f;                  // m is the row's, l this thread's half of the sum
+        // m: the maximum the row's exponentials, sum and output are relative to. It follows the true running maximum only
+        // when that has moved ahead by more than 8 (a factor of 256, harmless in float32 and bfloat16): only then is the
+        // output row in TMEM rescaled, which is rare after the first blocks. l: this thread's half of the row's sum.
+        float m = -CUDART_INF_F, l = 0.f;
         for (int j = 0; j < n_blocks; ++j) {
             const int b = j & 1, kb = kb_first + j * BKV, k0 = kb + half * HALF;
             const bool have = tc::mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag);
@@ -285,10 +285,25 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (*softmax_abort) break;                     // the same decision in all eight warps
             const float mx = fmaxf(xchg[r], xchg[BQ + r]);
             if (stamp) stamps[9 + 4 * j] = tc::global_ns();
-            const float m_new = fmaxf(m, mx * p.scale_log2e);      // the scale is positive
-            const float alpha = m_new == -CUDART_INF_F ? 1.f : exp2_approx(m - m_new);
-            const float msub = m_new == -CUDART_INF_F ? 0.f : m_new;
-            m = m_new;
+            const float m_true = fmaxf(m, mx * p.scale_log2e);     // the scale is positive
+            const bool move = m_true > m + 8.f || (m == -CUDART_INF_F && m_true != -CUDART_INF_F);
+            const float alpha = move ? exp2_approx(m - m_true) : 1.f;      // 0 from -inf
+            if (move) m = m_true;
+            const float msub = m == -CUDART_INF_F ? 0.f : m;
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // rescale this thread's 32 output dimensions in TMEM: P_{j-1} V_{j-1} must have been added first
+                if (!tc::mbar_wait(&o_full[0], (j - 1) & 1, abort_flag)) *softmax_abort = 1;
+                else {
+                    tc::fence_after_sync();
+                    uint32_t v[DH];
+                    tc::tmem_ld_x32(lane_addr + O_COL + half * DH, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < DH; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tc::tmem_st_x32(lane_addr + O_COL + half * DH, v);
+                    tc::tmem_st_wait();
+                }
+            }
             // exponentials (a masked score gives exactly 0), their sum, P as bfloat16 into shared memory (K-major,
             // 128-byte swizzle: 16-byte chunk c of row r lies at chunk c ^ (r & 7)); this thread's keys are one
             // 128-byte row of the block's half `half`
@@ -322,31 +337,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&p_ready[b]);
             if (stamp) stamps[10 + 4 * j] = tc::global_ns();
-            if (j > 0) {
-                // O = (O + P_{j-1} V_{j-1}) * alpha_j, this thread's 32 output dimensions
-                const int pb = (j - 1) & 1;
-                if (!tc::mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, abort_flag)) *softmax_abort = 1;
-                else {
-                    tc::fence_after_sync();
-                    uint32_t v[DH];
-                    tc::tmem_ld_x32(lane_addr + O_COL + pb * D + half * DH, v);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < DH; ++i) o[i] = (o[i] + __uint_as_float(v[i])) * alpha;
-                }
-            }
             if (stamp) stamps[11 + 4 * j] = tc::global_ns();
         }
-        // the last block's P.V, the two halves of the row sum, and the output row
+        // the output row after the last block's P.V, and the two halves of the row sum
         {
-            const int pb = (n_blocks - 1) & 1;
-            if (!*softmax_abort && !tc::mbar_wait(&o_full[pb], ((n_blocks - 1) >> 1) & 1, abort_flag)) *softmax_abort = 1;
+            if (!*softmax_abort && !tc::mbar_wait(&o_full[0], (n_blocks - 1) & 1, abort_flag)) *softmax_abort = 1;
             row_max[4 * BQ + half * BQ + r] = l;
             asm volatile("bar.sync 2, 256;" ::: "memory");
             if (!*softmax_abort) {
                 tc::fence_after_sync();
                 uint32_t v[DH];
-                tc::tmem_ld_x32(lane_addr + O_COL + pb * D + half * DH, v);
+                tc::tmem_ld_x32(lane_addr + O_COL + half * DH, v);
                 tc::tmem_ld_wait();
                 if (r < rows) {
                     const float sum = row_max[4 * BQ + r] + row_max[5 * BQ + r];
@@ -356,7 +357,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     for (int c = 0; c < DH; c += 8) {
                         float f[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) f[i] = (o[c + i] + __uint_as_float(v[c + i])) * inv;
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c + i]) * inv;
                         *reinterpret_cast<uint4*>(dst + c) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
                                                                           pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
                     }
