@@ -231,12 +231,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 tc::fence_after_sync();
                 if (stamps && j < 8) stamps[40 + 2 * j] = tc::global_ns();
                 const uint32_t v_addr = tc::smem_u32(sKV + s * STAGE_BYTES + TILE_BYTES);
-                const uint32_t p_addr = tc::smem_u32(sP + b * P_BYTES);
+                const uint32_t tmem_p = tmem_base + S_COL + b * BKV;     // P_j lies over the first 64 columns of S_j
                 const uint32_t tmem_o = tmem_base + O_COL;          // the output accumulates in TMEM over all blocks
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k)
-                    tc::mma_bf16(tmem_o, tc::smem_desc_sw128(p_addr + (k / 4) * TILE_BYTES + (k % 4) * 32),
-                                 tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    tc::mma_bf16_a_tmem(tmem_o, tmem_p + k * 8, tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o,
+                                        (j > 0 || k > 0) ? 1u : 0u);
                 tc::mma_commit(&o_full[0]);
                 tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
                 if (j + 2 < n_blocks) issue_scores(j + 2);   // its score buffer is free: P_j exists
@@ -304,23 +304,19 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     tc::tmem_st_wait();
                 }
             }
-            // exponentials (a masked score gives exactly 0), their sum, P as bfloat16 into shared memory (K-major,
-            // 128-byte swizzle: 16-byte chunk c of row r lies at chunk c ^ (r & 7)); this thread's keys are one
-            // 128-byte row of the block's half `half`
+            // exponentials (a masked score gives exactly 0), their sum, and P as bfloat16 into tensor memory, over the
+            // first 64 columns of this block's scores (every thread of the row has its scores in registers since the
+            // exchange above): two consecutive keys per column, this thread's 64 keys in columns 32*half .. 32*half+31
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint8_t* p_row = sP + b * P_BYTES + half * TILE_BYTES + r * 128;
+            uint32_t packed[HALF / 2];
 #pragma unroll
-            for (int c = 0; c < HALF / 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(sv[8 * c + 2 * i]), p.scale_log2e, -msub));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), p.scale_log2e, -msub));
-                    sum4[i] += p0 + p1;
-                    w[i] = pack_bf16(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int i = 0; i < HALF / 2; ++i) {
+                const float p0 = exp2_approx(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2e, -msub));
+                const float p1 = exp2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2e, -msub));
+                sum4[i & 3] += p0 + p1;
+                packed[i] = pack_bf16(p0, p1);
             }
+            tc::tmem_st_x32(lane_addr + S_COL + b * BKV + half * (HALF / 2), packed);
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (kb + BKV - 1 > pos_last) {
                 // value rows of keys past the tile's last query: unwritten cache slots, to be zeros under P = 0
@@ -332,8 +328,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     for (int i = 0; i < 8; ++i) z[i] = make_uint4(0, 0, 0, 0);
                 }
             }
-            tc::fence_proxy_async();          // P (and the zeroed rows) to the proxy the MMA reads through
-            tc::fence_before_sync();          // this thread's TMEM reads of S are done
+            tc::tmem_st_wait();               // P is in tensor memory
+            tc::fence_proxy_async();          // the zeroed value rows to the proxy the MMA reads through
+            tc::fence_before_sync();          // this thread's TMEM reads and writes are done
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&p_ready[b]);
             if (stamp) stamps[10 + 4 * j] = tc::global_ns();
