@@ -1,19 +1,22 @@
 // Prompt-portion attention on the tcgen05 tensor cores, for bfloat16 caches and head size 64.
 //
 // A block owns 128 consecutive query tokens of one request and one head and walks the request's keys in blocks
-// of 128 straight out of the cache pages. Three roles:
-//   warp 0      TMA: the query tile once, then per key block one box per cache page for the keys and one for
-//               the values (each lane issues one box), several blocks ahead;
+// of 128. Three roles:
+//   warp 0      TMA: the query tile once, then per key block either one box per cache page for the keys and one
+//               for the values (each lane issues one box), or, for a block that lies wholly in this step, one box
+//               of 128 rows each straight from the projection's output; several blocks ahead;
 //   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, accumulator in TMEM, two buffers so that the
-//               scores of block j+2 are computed while the softmax works on j and j+1), then O_j = P_j V_j
-//               (128 x 64) from the probabilities that the softmax warps left in shared memory; V is read as it
-//               lies in the cache, as an MN-major operand;
+//               scores of block j+2 are computed while the softmax works on j and j+1), then O += P_j V_j
+//               (128 x 64, accumulated in TMEM over all blocks) with P read from tensor memory and V read as it
+//               lies in memory, as an MN-major operand;
 //   warps 2..9  softmax: two threads own one query row (its TMEM lane), one for each half of a block's 128 keys,
 //               so only the two halves' maxima are exchanged (shared memory, one barrier per block) and nothing is
-//               shuffled; a thread takes its 64 scores into registers with two TMEM loads in flight, writes P as
-//               bfloat16 in the swizzled K-major layout the MMA reads, and keeps half of the output row in
-//               registers: O = (O + P_{j-1} V_{j-1}) * exp2(m_{j-1} - m_j), float32 throughout. With one thread per
-//               row (four warps) a block cost the softmax 1.3 us against 0.3 us of MMAs.
+//               shuffled; a thread takes its 64 scores into registers with two TMEM loads in flight and writes P
+//               as bfloat16 pairs into tensor memory, over the first columns of the scores it came from. The
+//               exponentials, the row sum and the output are relative to a maximum that follows the true running
+//               maximum only when that has moved ahead by more than 8 (a factor of 256): only then does a thread
+//               rescale its half of the output row in TMEM, which is rare after the first blocks; the result is
+//               the same, since the sum is kept relative to the same maximum. float32 throughout.
 // Scores, softmax and the weighted sum of values are float32 (damendaemon/kernels.py:147-178 for the mask and
 // the stable softmax; damendaemon/qwen2.py:754-770 for the offset-aware causal rule). Keys outside the live
 // range (beyond the last query of the tile, before the window, pages that were given back) are never multiplied
@@ -28,9 +31,8 @@ namespace {
 constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 64 + 256, STAGES = 4;
 constexpr int TILE_BYTES = BKV * D * 2;             // one 128 x 64 bf16 tile: 16 KB
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // keys, then values
-constexpr int P_BYTES = 2 * TILE_BYTES;             // 128 x 128 probabilities as two 64-key halves
 constexpr int EXCHANGE_BYTES = 6 * BQ * 4;           // row maxima of the two halves (two buffers), then the two row sums
-constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024 + 256 + EXCHANGE_BYTES;
+constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 1024 + 256 + EXCHANGE_BYTES;
 constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O: 64 columns
 constexpr int S_COL = 0, O_COL = 256;
 
@@ -75,8 +77,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sQ = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sKV = sQ + TILE_BYTES;
-    uint8_t* sP = sKV + STAGES * STAGE_BYTES;
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(sKV + STAGES * STAGE_BYTES);
     uint64_t* kv_empty = kv_full + STAGES;
     uint64_t* q_full = kv_empty + STAGES;
     uint64_t* s_full = q_full + 1;        // [2]
@@ -85,7 +86,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* softmax_abort = abort_flag + 1;          // written by softmax threads only, read after their barrier
-    float* row_max = reinterpret_cast<float*>(sP + 2 * P_BYTES + 256);
+    float* row_max = reinterpret_cast<float*>(sKV + STAGES * STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, kh = h / (p.H / p.KH);
