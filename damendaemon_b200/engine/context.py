@@ -50,6 +50,7 @@ class StepContext:
             # with 25 heads and 768 keys: faster than the row kernel from 8 tokens on (11.6 against 14.0 us; 54 against 68
             # at 64), slower at 4 and below (11.0 against 9.8 us; 9.1 against 5.5 at one token), hence the threshold
             splits = kernels.attention_decode_pages_splits(self.n_tokens, n_heads, kv.shape[3], self.split_context, q.device)
+            splits = max(splits, -(-table.shape[1] // 128))          # a block holds the ids of at most 128 pages
             return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                             n_splits=splits, k_new=k if cache.writable else None,
                                             v_new=v if cache.writable else None, kernel="pages")
