@@ -98,10 +98,18 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ row_in
                      TO* __restrict__ out, int width, float eps) {
     __shared__ float scratch[4];
     dd_launch_dependents();
-    dd_grid_wait();
     const int row = blockIdx.x;
-    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * width);
     const int n4 = width >> 2;
+    // gamma and beta are weights: they are in registers before the kernel that produces x has finished
+    float4 g[VPT], b[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        g[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(gamma) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        b[i] = (beta && c < n4) ? __ldg(reinterpret_cast<const float4*>(beta) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    dd_grid_wait();
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * width);
     float4 v[VPT];
     float sum = 0.f;
 #pragma unroll
@@ -121,17 +129,12 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ row_in
     }
     const float rstd = 1.0f / sqrtf(block_sum<128>(sq, scratch) / (float)width + eps);
     TO* o = out + (size_t)row * width;
-    const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(beta);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * 128;
-        if (c < n4) {
-            const float4 g = g4[c];
-            const float4 b = beta ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-            Pack4<TO>::store(o + 4 * c, (v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
-                             (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
-        }
+        if (c < n4)
+            Pack4<TO>::store(o + 4 * c, (v[i].x - mean) * rstd * g[i].x + b[i].x, (v[i].y - mean) * rstd * g[i].y + b[i].y,
+                             (v[i].z - mean) * rstd * g[i].z + b[i].z, (v[i].w - mean) * rstd * g[i].w + b[i].w);
     }
 }
 
