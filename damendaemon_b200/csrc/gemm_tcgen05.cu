@@ -86,7 +86,8 @@ template <int BN> struct ClusterConfig {
     static constexpr int A_BYTES = Config<BN>::A_BYTES;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     static constexpr int REDUCE_BYTES = (BM + 8) * BN * 4;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + REDUCE_BYTES;
+    static constexpr int BIAS_BYTES = BM * 4;               // the bias of this block's slice of features
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + REDUCE_BYTES + BIAS_BYTES;
 };
 
 // Ask L2 to fetch this block's share of p.prefetch (16-byte granules, 32 KB per request).
@@ -803,9 +804,16 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     __syncwarp();
     tc::cluster_wait();          // every block of the cluster is up: remote shared memory may be written
 
+    // The bias of the features this block will finish is a weight: it is fetched into shared memory now, while the
+    // weights stream, instead of costing a trip to L2 at the very end of the block.
+    float* bias_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(reduce_buf) + C::REDUCE_BYTES);
     if (warp >= 2) {
         const int quarter = warp & 3;
         const int f = quarter * 32 + lane;                // feature of the tile this thread holds in TMEM
+        {
+            const int n = n0 + rank * slice + f;
+            bias_s[f] = (p.bias && f < slice && n < p.N) ? __ldg(p.bias + n) : 0.f;
+        }
         const bool have = n_kblocks > 0 && tc::mbar_wait(tmem_full_bar, 0, abort_flag);
         tc::fence_after_sync();
         if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 5] = tc::global_ns();
@@ -857,7 +865,7 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 if (n >= p.N || m >= p.M) continue;
                 float v = 0.f;
                 for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
-                if (p.bias) v += p.bias[n];
+                v += bias_s[lf];
                 v = activation_for(v, p.act, p.out_dtype) + res[u];
                 if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
                 else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
