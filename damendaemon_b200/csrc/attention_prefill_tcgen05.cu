@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const __grid_constant__ CUtensorMap map_k_new, const __grid_constant__ CUtensorMap map_v_new,
                                  const AttnParams p) {
+    dd_launch_dependents();
     // which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once.
     int e = 0, tile = blockIdx.x, len = 0;
     for (; e < p.n_entries; ++e) {
@@ -113,6 +114,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         *softmax_abort = 0;
         tc::fence_barrier_init();
         tc::fence_proxy_async();
+        tc::prefetch_tensormap(&map_q);
+        tc::prefetch_tensormap(&map_kv);
+        tc::prefetch_tensormap(&map_k_new);
+        tc::prefetch_tensormap(&map_v_new);
     }
     if (warp == 1) {
         tc::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -124,15 +129,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t tmem_base = *tmem_slot;
     unsigned long long* stamps = p.timeline ? p.timeline + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 64 : nullptr;
     if (stamps && threadIdx.x == 0) stamps[0] = tc::global_ns();
-    dd_launch_dependents();
     dd_grid_wait();              // queries and the cache are earlier kernels' results
     if (stamps && threadIdx.x == 0) stamps[1] = tc::global_ns();
 
     if (warp == 0) {
         // ---- TMA ----
         if (lane == 0) {
-            tc::prefetch_tensormap(&map_q);
-            tc::prefetch_tensormap(&map_kv);
             tc::mbar_expect_tx(q_full, TILE_BYTES);
             tc::tma_load_2d(sQ, &map_q, h * D, row0, q_full);       // rows past the last token read as zeros
         }

@@ -186,11 +186,10 @@ __device__ __forceinline__ void load_residual_row16(const GemmParams& p, int m, 
     }
 }
 
-template <int ACT, bool BF16_OUT, bool RESIDUAL>
-__device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
-    const bool whole = p.vec && n_first + 16 <= p.N;
-    float v[16];
-    if (p.bias && whole) {
+// The bias of 16 consecutive features (zeros without one): the same for every thread, asked for while the accumulator
+// is still on its way from TMEM, like the residual values.
+__device__ __forceinline__ void load_bias16(const GemmParams& p, int n_first, float* v) {
+    if (p.bias && p.vec && n_first + 16 <= p.N) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + n_first) + q);
@@ -200,6 +199,11 @@ __device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_fi
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = (p.bias && n_first + j < p.N) ? __ldg(p.bias + n_first + j) : 0.f;
     }
+}
+
+template <int ACT, bool BF16_OUT, bool RESIDUAL>
+__device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r, float* v) {
+    const bool whole = p.vec && n_first + 16 <= p.N;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         float u = __uint_as_float(acc[j]) + v[j];
@@ -246,21 +250,22 @@ __device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_fi
 }
 
 template <int ACT, bool BF16_OUT>
-__device__ __forceinline__ void store_row16_r(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
-    if (p.residual) store_row16<ACT, BF16_OUT, true>(p, m, n_first, acc, r);
-    else store_row16<ACT, BF16_OUT, false>(p, m, n_first, acc, r);
+__device__ __forceinline__ void store_row16_r(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r, float* v) {
+    if (p.residual) store_row16<ACT, BF16_OUT, true>(p, m, n_first, acc, r, v);
+    else store_row16<ACT, BF16_OUT, false>(p, m, n_first, acc, r, v);
 }
 
 template <int ACT>
-__device__ __forceinline__ void store_row16_o(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
-    if (p.out_dtype == DD_BF16) store_row16_r<ACT, true>(p, m, n_first, acc, r);
-    else store_row16_r<ACT, false>(p, m, n_first, acc, r);
+__device__ __forceinline__ void store_row16_o(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r, float* v) {
+    if (p.out_dtype == DD_BF16) store_row16_r<ACT, true>(p, m, n_first, acc, r, v);
+    else store_row16_r<ACT, false>(p, m, n_first, acc, r, v);
 }
 
-__device__ __forceinline__ void store_out_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r) {
-    if (p.act == DD_ACT_NONE) store_row16_o<DD_ACT_NONE>(p, m, n_first, acc, r);
-    else if (p.act == DD_ACT_GELU_NEW) store_row16_o<DD_ACT_GELU_NEW>(p, m, n_first, acc, r);
-    else store_row16_o<DD_ACT_GELU_ERF>(p, m, n_first, acc, r);
+// v: the bias of the 16 features (load_bias16); it is used up as scratch
+__device__ __forceinline__ void store_out_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r, float* v) {
+    if (p.act == DD_ACT_NONE) store_row16_o<DD_ACT_NONE>(p, m, n_first, acc, r, v);
+    else if (p.act == DD_ACT_GELU_NEW) store_row16_o<DD_ACT_GELU_NEW>(p, m, n_first, acc, r, v);
+    else store_row16_o<DD_ACT_GELU_ERF>(p, m, n_first, acc, r, v);
 }
 
 // One SM per tile, persistent over tiles, two accumulators in TMEM so that the epilogue of one tile runs under the
@@ -434,10 +439,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int c0 = c_begin; c0 < c_limit && b0 + c0 < rows_b; c0 += 16) {
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
-                    float res[16];
+                    float res[16], bias16[16];
                     if (row_ok) {                                        // in flight while the accumulator is read
-                        if (BY_TOKEN) load_residual_row16(p, row, b0 + c0, res);
-                        else load_residual16(p, b0 + c0, row, res);
+                        if (BY_TOKEN) {
+                            load_residual_row16(p, row, b0 + c0, res);
+                            load_bias16(p, b0 + c0, bias16);
+                        } else load_residual16(p, b0 + c0, row, res);
                     }
                     tc::tmem_ld_wait();
                     if (c0 + 16 >= c_limit || b0 + c0 + 16 >= rows_b) {  // this warp's last read of the accumulator
@@ -446,7 +453,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
                     }
                     if (row_ok) {
-                        if (BY_TOKEN) store_out_row16(p, row, b0 + c0, r, res);
+                        if (BY_TOKEN) store_out_row16(p, row, b0 + c0, r, res, bias16);
                         else {
                             float accv[16];
 #pragma unroll
@@ -666,14 +673,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 uint32_t r[16];
                 tc::tmem_ld_x16(lane_addr + c0, r);
                 float res[16];
-                if (m_ok) load_residual_row16(p, m, b0 + c0, res);    // in flight while the accumulator is read
+                float bias16[16];
+                if (m_ok) {                                           // in flight while the accumulator is read
+                    load_residual_row16(p, m, b0 + c0, res);
+                    load_bias16(p, b0 + c0, bias16);
+                }
                 tc::tmem_ld_wait();
                 if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
                 }
-                if (m_ok) store_out_row16(p, m, b0 + c0, r, res);
+                if (m_ok) store_out_row16(p, m, b0 + c0, r, res, bias16);
             }
         }
     }

@@ -12,11 +12,12 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
                                 T* __restrict__ cache, int n_pages, int kv_heads, int page_size, int head_dim,
                                 int* __restrict__ error_flag) {
     dd_launch_dependents();
-    dd_grid_wait();
+    // positions, entries and the block table are the step's inputs: the page is known before the projection has finished
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int block = pos / page_size;
     int page = (pos >= 0 && block < max_blocks) ? block_table[(size_t)tok_entry[t] * max_blocks + block] : -1;
+    dd_grid_wait();
     if (page < 0 || page >= n_pages) {
         if (threadIdx.x == 0) atomicOr(error_flag, 2);
         return;
