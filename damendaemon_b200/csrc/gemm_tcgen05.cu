@@ -726,6 +726,7 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     float* reduce_buf = reinterpret_cast<float*>(tiles + C::STAGES * C::STAGE_BYTES + 256);
 
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 0] = tc::global_ns();
+    dd_launch_dependents();      // the next kernel may begin its own set-up (and ask for its weights) at once
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = (int)tc::cluster_size();
     const int rank = (int)tc::cluster_rank();
@@ -757,7 +758,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 1] = tc::global_ns();
-    dd_launch_dependents();
     tc::cluster_arrive();        // "my shared memory exists": waited for before the first remote write
 
     if (warp == 0) {
