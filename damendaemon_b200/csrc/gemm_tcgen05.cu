@@ -149,8 +149,7 @@ __device__ __forceinline__ void load_residual16(const GemmParams& p, int m_first
 }
 
 // r: residual values already loaded (load_residual16), issued by the caller before it waits for the accumulator.
-__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc, const float* r) {
-    const float b = p.bias ? p.bias[n] : 0.f;
+__device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc, const float* r, float b) {
     if (p.act == DD_ACT_NONE) store16_o<DD_ACT_NONE>(p, m_first, n, acc, b, r);
     else if (p.act == DD_ACT_GELU_NEW) store16_o<DD_ACT_GELU_NEW>(p, m_first, n, acc, b, r);
     else store16_o<DD_ACT_GELU_ERF>(p, m_first, n, acc, b, r);
@@ -159,7 +158,7 @@ __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, in
 __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc) {
     float r[16];
     load_residual16(p, m_first, n, r);
-    store_out16(p, m_first, n, acc, r);
+    store_out16(p, m_first, n, acc, r, p.bias ? p.bias[n] : 0.f);
 }
 
 // ---- epilogue of tiles whose accumulator lanes are tokens (tiles of 128 tokens x BN features) ----
@@ -424,6 +423,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t acc = local & 1;
             const int row = a0 + quarter * 32 + lane;      // this thread's token (BY_TOKEN) or output feature
             const bool row_ok = row < rows_a;
+            // the bias of this thread's feature is a weight: it is on its way before the accumulator is waited for
+            const float feature_bias = (!BY_TOKEN && row_ok && p.bias) ? __ldg(p.bias + row) : 0.f;
             if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*epilogue_abort) break;                   // the same decision in all eight warps
@@ -458,7 +459,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             float accv[16];
 #pragma unroll
                             for (int j = 0; j < 16; ++j) accv[j] = __uint_as_float(r[j]);
-                            store_out16(p, b0 + c0, row, accv, res);
+                            store_out16(p, b0 + c0, row, accv, res, feature_bias);
                         }
                     }
                 }
@@ -1027,7 +1028,10 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
     const int kblocks = dd_ceil_div(K, BK);
     const bool long_k = kblocks > 32;                 // more than 2,048: worth splitting even for 17 to 64 tokens
     int bn = 128;
-    if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = long_k ? 64 : 32;
+    // 33 to 64 tokens: two tiles of 32 tokens double the blocks, which pays while the feature tiles alone do not fill the
+    // GPU; a matrix with more feature tiles than SMs (the LM head) would only be streamed twice (55 against 33 us)
+    const bool many_tiles = dd_ceil_div(N, BM) >= sm_count;
+    if (M <= 16) bn = 16; else if (M <= 32) bn = 32; else if (M <= 64) bn = (long_k || many_tiles) ? 64 : 32;
     else {
         // Tiles of 128 tokens x c features on one SM, or of 256 tokens x c features on a pair of SMs (less L2
         // traffic per flop). A round of one tile per SM was measured to take about as long as c + 64 columns
