@@ -57,7 +57,7 @@ __device__ __forceinline__ void mma_bf16_row0(float& c0, float& c1, uint32_t a0,
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
                  : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
                  : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
-    (void)d2, (void)d3;
+    asm volatile("" ::"f"(d2), "f"(d3));      // the two dead accumulators count as used
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
