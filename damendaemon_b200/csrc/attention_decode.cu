@@ -170,13 +170,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     int pages[STAGES][STEPS];          // of the tiles about to be issued; the loop below is unrolled over its slots
 #pragma unroll
     for (int i = 0; i < STAGES; ++i) lookup(i, pages[i]);
-    // The first tiles are requested while the projection that produces the query is still running: the cache holds
-    // earlier steps' keys and values. Only the tile with the token's own position takes its row from k_new/v_new and
-    // has to wait, and with it every tile after it (copy groups complete in order).
+    // The first tiles are requested while the projection that produces the query is still running: with k_new/v_new
+    // given, everything before the token's own position was written by earlier steps. Only the tile with that position
+    // takes its row from k_new/v_new and has to wait, and with it every tile after it (copy groups complete in order).
+    // Without k_new/v_new the row of this step is in the cache already, written by some kernel of this step: then
+    // nothing is read before the wait.
     int issued = 0;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        const bool early = issued == i && (k_new == nullptr || first_key + i * WARPS * TILE + TILE <= pos);
+        const bool early = issued == i && k_new != nullptr && first_key + i * WARPS * TILE + TILE <= pos;
         if (early) {
             if (i < n_tiles) issue(i, pages[i]);
             cp_commit();

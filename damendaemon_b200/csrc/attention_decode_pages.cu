@@ -119,11 +119,14 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
         tc::tma_load_2d(dst, &map_kv, 0, ((page * 2 + 0) * p.H + head0) * p.P, &full[s]);
         tc::tma_load_2d(dst + box_bytes, &map_kv, 0, ((page * 2 + 1) * p.H + head0) * p.P, &full[s]);
     };
-    // The pages hold earlier steps' keys and values (this step's own row is patched in from k_new below), so the first
-    // stages are requested while the projection that produces the queries is still running.
-    if (threadIdx.x == 0)
+    // With k_new/v_new given the pages hold earlier steps' keys and values only (this step's own row is patched in
+    // below), so the first stages are requested while the projection that produces the queries is still running.
+    // Without them the step's row is in the cache already, written by some kernel of this step: then the wait comes first.
+    if (threadIdx.x == 0 && p.k_new != nullptr)
         for (int i = 0; i < min(n_mine, p.stages); ++i) load_page(i);
     dd_grid_wait();              // the queries and this step's keys and values are the kernel before this one's work
+    if (threadIdx.x == 0 && p.k_new == nullptr)
+        for (int i = 0; i < min(n_mine, p.stages); ++i) load_page(i);
 
     // the queries of this warp's heads as A operands: row 0 of a 16-row tile, every other row zero
     uint32_t qf[HEADS_PER_WARP][D / 16][2];
