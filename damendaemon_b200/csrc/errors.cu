@@ -39,3 +39,12 @@ DD_API int dd_device_arch() {
     cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
     return major * 10 + minor;
 }
+
+// One asynchronous copy of `bytes` bytes from pinned host memory to the device, in stream order: the step's
+// metadata, without a framework call in between.
+DD_API int dd_copy_to_device(void* dst, const void* src, long long bytes, void* stream) {
+    if (bytes <= 0) return 0;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    if (e != cudaSuccess) return dd_fail("dd_copy_to_device: %s", cudaGetErrorString(e));
+    return 0;
+}

@@ -97,6 +97,9 @@ class Engine:
         self._meta_dev = None
         self._meta_host = []
         self._meta_events = []
+        self._meta_numpy = []
+        self._meta_recorded = [False, False]
+        self._arange = np.arange(max_requests + 2, dtype=np.int32)
         self._turn = 0
         self.steps = 0
         self.tokens_run = 0
@@ -173,11 +176,13 @@ class Engine:
             torch.cuda.current_stream().synchronize()
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-            self._meta_events = [None, None]
+            self._meta_numpy = [h.numpy() for h in self._meta_host]
+            self._meta_events = [torch.cuda.Event(), torch.cuda.Event()]
+            self._meta_recorded = [False, False]
             self._graphs.clear()                 # graphs hold views of the old buffer
         self._turn ^= 1
-        if self._meta_events[self._turn] is not None:
-            self._meta_events[self._turn].synchronize()
+        if self._meta_recorded[self._turn]:
+            self._meta_events[self._turn].synchronize()      # the copy out of this host buffer two steps ago is done
         return self._meta_host[self._turn]
 
     def _layout(self, N, E, M):
@@ -197,6 +202,26 @@ class Engine:
         MB = self.cache.max_blocks
         ids, pos, ent = (arr[at[k][0]:at[k][1]] for k in ("ids", "pos", "ent"))
         want, slot, start, pos0 = (arr[at[k][0]:at[k][1]] for k in ("want", "slot", "start", "pos0"))
+        if N == E:
+            # one token per entry (a decode step): whole arrays at once instead of an entry at a time
+            cache = self.cache
+            p0s = [cache.length[e.request] for e in entries]
+            slots = [cache.slot_of[e.request] for e in entries]
+            ids[:] = [e.tokens[0] for e in entries]
+            pos[:] = p0s
+            pos0[:] = p0s
+            ent[:] = self._arange[:E]
+            start[:] = self._arange[:E + 1]
+            slot[:] = slots
+            wi = 0
+            for i, e in enumerate(entries):
+                if e.want:                      # [0] or nothing
+                    want[wi] = i
+                    wi += 1
+            for g in cache.groups:
+                a, b = at["table:" + g.name]
+                arr[a:b].reshape(E, MB)[:] = g.table_array[slots]
+            return slots, p0s
         cursor, wi, slots = 0, 0, []
         for i, e in enumerate(entries):
             n = lengths[i]
@@ -230,12 +255,11 @@ class Engine:
 
     def _upload(self, entries, lengths, at):
         host = self._meta_buffers(at["total"])
-        slots, pos0 = self._fill(entries, lengths, at, host.numpy())
-        self._meta_dev[:at["total"]].copy_(host[:at["total"]], non_blocking=True)
+        slots, pos0 = self._fill(entries, lengths, at, self._meta_numpy[self._turn])
+        kernels.copy_to_device(self._meta_dev, host, at["total"] * 4)
         self.last_h2d_bytes = at["total"] * 4
-        event = torch.cuda.Event()
-        event.record()
-        self._meta_events[self._turn] = event
+        self._meta_events[self._turn].record()
+        self._meta_recorded[self._turn] = True
         return slots, pos0
 
     def _run(self, entries):

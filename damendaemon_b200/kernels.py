@@ -26,6 +26,7 @@ class KernelError(RuntimeError):
 _SIGNATURES = {
     "core": {
         "dd_device_arch": [],
+        "dd_copy_to_device": [_c_void, _c_void, ctypes.c_longlong, _c_void],
         "dd_embed": [_c_void] * 5 + [_c_int] * 5 + [_c_void, _c_void],
         "dd_layernorm": [_c_void] * 5 + [_c_int, _c_int, _c_float, _c_int, _c_void],
         "dd_gemm_simt": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
@@ -144,6 +145,13 @@ def error_flag(device):
     if key not in _error_flags:
         _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _error_flags[key]
+
+
+def copy_to_device(dst, src, n_bytes):
+    """One asynchronous host-to-device copy on the current stream, from pinned memory (src) into dst: the step's
+    metadata. Not counted as a kernel launch."""
+    global launches
+    _call(library("core"), "dd_copy_to_device", dst.data_ptr(), src.data_ptr(), int(n_bytes), _stream(), n_kernels=0)
 
 
 def read_error_flag(device):
