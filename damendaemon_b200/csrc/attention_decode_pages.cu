@@ -3,11 +3,11 @@
 //
 // In the cache a page holds the keys of all heads side by side and then the values ([page][K|V][head][slot][64]):
 // the keys of G neighbouring heads are one run of G x page_size rows of 128 bytes. A block owns (token, group of
-// G <= 16 heads, split of the token's pages); thread 0 asks TMA for one box of G x page_size rows of keys and one
-// of values per page, two pages ahead, so a block moves its bytes in pieces of tens of KB with two instructions
+// G <= 8 heads, split of the token's pages); thread 0 asks TMA for one box of G x page_size rows of keys and one
+// of values per page, as many pages ahead as the ring holds, so a block moves its bytes in pieces of tens of KB with two instructions
 // each (copying the same bytes 16 at a time, one key row per 8 lanes, the memory system delivered 4.5 TB/s;
 // in boxes of this size it delivers 5.4). The 128-byte swizzle of the tensor map is the layout ldmatrix wants.
-// Each of the 8 warps owns up to two heads of the group for all pages, so nothing is merged inside the block:
+// Each of the 8 warps owns one head of the group for all pages, so nothing is merged inside the block:
 // scores and P.V on mma.sync m16n8k16 with the single query in row 0 (see attention_decode.cu), running maximum
 // and sum in float32, base 2 (damendaemon/kernels.py:147-178; split merge by log-sum-exp kernels.py:190-210).
 //

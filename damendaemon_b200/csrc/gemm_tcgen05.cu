@@ -1,25 +1,31 @@
 // bfloat16 GEMM on the 5th-generation tensor cores: out[M,N] = act(X[M,K] . W[N,K]^T + bias) (+ residual).
 //
-// The product is computed transposed, D^T = W . X^T: the weight rows (output features)
-// are the 128-row M side of tcgen05.mma and the tokens its N side (16..256), so the same
-// kernel serves a decode step of a few tokens (narrow N tile, split over K to fill the
-// SMs while the weights stream from HBM once) and a prompt portion of thousands (N tile
-// 256). In TMEM the accumulator has one output feature per lane and one token per
-// column; an epilogue thread therefore owns one feature, its bias is one register, and a
-// warp's 32 lanes write 32 consecutive features of a token row: coalesced stores with no
-// staging through shared memory.
+// Three kernels share the pipeline (TMA loads of 64-element k slices with the 128-byte swizzle into a ring of
+// stages guarded by full/empty mbarriers; one thread issuing tcgen05.mma from shared-memory descriptors and
+// releasing stages with tcgen05.commit; epilogue warps reading the accumulator with tcgen05.ld) and differ in
+// which operand is the 128-row side of the instruction and in how the work is spread:
 //
-// The kernel is persistent: at most one CTA per SM walks over (tile, split) work items, the TMA
-// producer runs ahead across items, and the accumulator is double buffered in TMEM so that the
-// epilogue of one tile overlaps the MMAs of the next.
+//   by feature (token tiles of 16, 32 or 64): the product is computed transposed, D^T = W . X^T. The weight rows
+//   (output features) are the 128 lanes of the accumulator and the tokens its columns, so a step of a few tokens
+//   wastes no tensor-core rows; an epilogue thread owns one feature, its bias is one register, and a warp's 32
+//   lanes write 32 consecutive features of a token row. Up to 64 tokens this is the cluster kernel: a cluster of
+//   CTAs splits K, every CTA streams its share of the weight tile, and the partial tiles are summed over
+//   distributed shared memory in a fixed order (deterministic), so the weights come from HBM once while all
+//   SMs pull. Above 64 tokens the persistent kernel may use these tiles too (with a workspace split over K).
 //
-// Pipeline per CTA: warp 0 issues TMA loads (W tile 128x64 and X tile BNx64 bf16, 128-byte
-// swizzle) into a ring of stages guarded by full/empty mbarriers; warp 1 allocates TMEM
-// and issues tcgen05.mma from shared-memory descriptors, releasing stages with
-// tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld and apply the epilogue.
-// With split-K each CTA writes its float32 partial tile to a workspace; the CTA that
-// arrives last at the tile's counter sums the partials in split order (deterministic) and
-// applies the epilogue, then resets the counter for the next launch.
+//   by token (token tiles of 128, persistent kernel): D = X . W^T, 128 tokens are the lanes and 128, 192 or 256
+//   features the columns; an epilogue thread owns a token row and writes 16 features at a time as 16-byte
+//   stores, with the residual read the same way. At most one CTA per SM walks over the tiles, the producer
+//   runs ahead across tiles and the accumulator is double buffered in TMEM, so the epilogue of one tile
+//   overlaps the MMAs of the next; eight epilogue warps, two per lane quarter, share a tile's columns.
+//
+//   two SMs per tile (pair kernel): tcgen05.mma.cta_group::2 over 256 tokens x up to 256 features; each CTA of
+//   the pair loads its 128 tokens and half of the weight tile, so a weight byte is read into shared memory once
+//   per 256 tokens.
+//
+// dd_gemm_tcgen05_plan chooses among them from the shape by counting rounds of tiles over the SMs.
+// Weights, bias and everything else that does not come from the kernel before are fetched before
+// griddepcontrol.wait, so that under programmatic dependent launch they overlap the previous kernel's tail.
 //
 // Every mbarrier wait is bounded (tcgen05.cuh); on a timeout the kernel sets bit 8 of the
 // error word, stops waiting everywhere, frees its TMEM and returns.
