@@ -22,6 +22,8 @@
 // range (beyond the last query of the tile, before the window, pages that were given back) are never multiplied
 // in: their scores are replaced, not scaled, and their value rows are zeroed in shared memory, so that stale
 // cache contents of any bit pattern cannot reach the result.
+// On request (store_new) the block also writes its tile's keys and values into the cache pages, by TMA from the
+// shared memory they were loaded into, which saves the cache-write kernel and its pass over the projection's output.
 // Every wait is bounded; a wait that runs out sets the error flag and the block leaves through the common exit.
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -45,6 +47,7 @@ struct AttnParams {
     int n_entries, max_blocks, out_stride, H, KH, P, n_pages, window;
     float scale_log2e;
     int new_rows;                   // 1: this step's keys and values are also at hand as rows beside the queries
+    int store_new;                  // 1: the kernel itself puts those rows into the cache (every entry starts on a key-block boundary)
     unsigned long long* timeline;   // null, or 64 time stamps (ns) per block: where a block's time goes
 };
 
@@ -206,6 +209,35 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) tc::mbar_expect_tx(&kv_full[s], (uint32_t)n_valid * page_bytes);
             if (stamps && lane == 0 && j < 8) stamps[56 + j] = tc::global_ns();
+        }
+        if (p.store_new && h % (p.H / p.KH) == 0) {
+            // This tile's own keys and values are the last key block, and they lie in shared memory in the layout of
+            // the cache's tensor map: TMA writes them into the tile's pages, one box per page, while the block works on
+            // them. No block of this launch reads these cache rows: with every entry starting on a key-block boundary,
+            // the key blocks that hold this step's tokens are read from k_new/v_new. A page that the entry fills only
+            // in part receives whatever follows the entry's last token in its other slots; slots past a request's
+            // length are never read by anyone.
+            if ((pos_first - q0) % BKV != 0) {
+                if (lane == 0) atomicOr(p.error_flag, 2);        // the caller broke the rule: nothing is written
+            } else {
+                const int j = n_blocks - 1, s = j % STAGES;
+                if (tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) {
+                    if (lane < 2 * pages_per_block) {
+                        const int slot = lane < pages_per_block ? lane : lane - pages_per_block;
+                        const bool values = lane >= pages_per_block;
+                        const int key0 = pos_first + slot * p.P;
+                        if (key0 <= pos_last) {
+                            const int page = bt[key0 / p.P];
+                            if (page < 0 || page >= p.n_pages) atomicOr(p.error_flag, 2);
+                            else
+                                tc::tma_store_2d(&map_kv, 0, ((page * 2 + (values ? 1 : 0)) * p.KH + kh) * p.P,
+                                                 sKV + s * STAGE_BYTES + (values ? TILE_BYTES : 0) + slot * page_bytes);
+                        }
+                    }
+                    tc::bulk_commit();
+                    tc::bulk_wait_all();         // shared memory has been read and the cache written before the block leaves
+                }
+            }
         }
     } else if (warp == 1) {
         // ---- MMA ----
@@ -420,10 +452,15 @@ DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, i
 
 // The arguments of dd_attention_prefill: entries are runs of consecutive tokens of one request; entry e holds
 // flattened tokens entry_start[e] .. entry_start[e+1]-1 at positions entry_pos0[e] ...; block_table row e is its
-// pages. cache [n_pages, 2, n_kv_heads, page_size, 64] bf16, which must hold this step's keys and values already.
+// pages. cache [n_pages, 2, n_kv_heads, page_size, 64] bf16, which must hold this step's keys and values already
+// unless store_new is set.
 // k_new/v_new: null, or this step's keys and values as rows of q_stride bf16 (kv head g at g*64), the same values
 // the cache holds: key blocks that lie wholly in this step are then read from there, one TMA box per block.
-DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, const void* cache, const int* entry_start,
+// store_new: the cache does not hold this step's keys and values yet; the kernel writes them from k_new/v_new
+// (dd_kv_store's work, done by TMA from the tiles in shared memory). Only for steps in which every entry starts at a
+// position that is a multiple of 128, so that no key block mixes cached and new keys (the caller's duty; an entry
+// that breaks it sets error bit 2 and writes nothing).
+DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, int store_new, void* cache, const int* entry_start,
                                         const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
                                         int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
                                         int head_dim, int page_size, int n_pages, int window, float scale,
@@ -445,6 +482,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     }
     if ((k_new == nullptr) != (v_new == nullptr) || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15))
         return dd_fail("dd_attention_prefill_tcgen05: k_new and v_new come together, 16-byte aligned");
+    if (store_new && !k_new) return dd_fail("dd_attention_prefill_tcgen05: store_new needs k_new and v_new");
     CUtensorMap map_q, map_kv, map_k_new, map_v_new;
     if (int e = make_map(&map_q, q, (unsigned long long)n_tokens, n_heads * D, q_stride, BQ, "the queries")) return e;
     // this step's keys and values as rows of the same stride as the queries (the fused projection's output), or the
@@ -460,6 +498,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
     p.timeline = g_timeline;
     p.new_rows = k_new != nullptr;
+    p.store_new = store_new != 0;
     // an upper bound of the number of 128-row tiles; blocks beyond the real count return at once
     dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, n_heads);
     dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, map_k_new, map_v_new, p);

@@ -24,6 +24,7 @@ class StepContext:
     host: dict = field(default_factory=dict)   # the same lists on the host, for parts that plan there
     decode_only: bool = False
     split_context: int = 0     # context length the key splits are planned for
+    aligned_starts: bool = False   # every entry starts at a multiple of the prompt attention's key block
     runtime: object = None
     sm_count: int = 148
 
@@ -59,15 +60,17 @@ class StepContext:
             return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                             n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=2),
                                             k_new=k if cache.writable else None, v_new=v if cache.writable else None)
-        if cache.writable:
+        tcgen05 = not self.decode_only and fast and self.runtime.attention != "mma" and \
+            kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype)
+        # the tcgen05 prompt kernel writes the cache itself when no key block mixes cached and new keys
+        fused_store = tcgen05 and cache.writable and self.aligned_starts
+        if cache.writable and not fused_store:
             kernels.kv_store(k, v, self.token_entry, self.positions, table, kv)
-        if not self.decode_only and fast:
-            if self.runtime.attention != "mma" and \
-                    kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype):
-                return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window,
-                                                 kernel="tcgen05", k_new=k if cache.writable else None,
-                                                 v_new=v if cache.writable else None)
-            if kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
-                return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
+        if tcgen05:
+            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window,
+                                             kernel="tcgen05", k_new=k if cache.writable else None,
+                                             v_new=v if cache.writable else None, store_new=fused_store)
+        if not self.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
+            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
         return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
                                       n_splits=self.key_splits(n_heads))

@@ -242,7 +242,7 @@ class Engine:
             arr[a:b].reshape(E, MB)[:] = g.table_array[slots]
         return slots, [int(x) for x in pos0]
 
-    def _context(self, N, E, M, at, decode_only, split_context, host=None):
+    def _context(self, N, E, M, at, decode_only, split_context, host=None, aligned=False):
         dev, MB = self._meta_dev, self.cache.max_blocks
         view = lambda k: dev[at[k][0]:at[k][1]]
         return StepContext(
@@ -251,7 +251,7 @@ class Engine:
             entry_pos0=view("pos0"),
             block_tables={g.name: view("table:" + g.name).view(E, MB) for g in self.cache.groups},
             host=host or {}, decode_only=decode_only, split_context=split_context, runtime=self.runtime,
-            sm_count=self.sm_count)
+            sm_count=self.sm_count, aligned_starts=aligned)
 
     def _upload(self, entries, lengths, at):
         host = self._meta_buffers(at["total"])
@@ -269,14 +269,16 @@ class Engine:
         decode_only = N == E
         slots, pos0 = self._upload(entries, lengths, at)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
+        block = kernels.ATTENTION_PREFILL_TCGEN05_KEY_BLOCK
+        aligned = not decode_only and all(p % block == 0 for p in pos0)
         if self.use_graph and M > 0 and N <= self.max_graph_tokens:
             # Every kernel reads lengths, positions and page tables from the metadata buffer, and launch shapes
             # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.
-            key = (N, E, M, decode_only)
+            key = (N, E, M, decode_only, aligned)
             graph = self._graphs.get(key)
             if graph is None and key in self._seen:
                 # the second step of this shape: capture it (the first ran eagerly and warmed everything up)
-                ctx = self._context(N, E, M, at, decode_only, self.max_context)
+                ctx = self._context(N, E, M, at, decode_only, self.max_context, aligned=aligned)
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.current_stream().synchronize()
                 with torch.cuda.graph(graph):
@@ -289,7 +291,7 @@ class Engine:
                 graph[0].replay()
                 return graph[1]             # valid until the next step of this shape
             self._seen.add(key)
-        ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host)
+        ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
         return self.model.forward(ctx, self._caches)
 
     @torch.no_grad()

@@ -60,19 +60,19 @@ def _decode_case(batch, context, dev, kernel="pages"):
     return run, {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
 
 
-def _prefill_case(prompts, length, dev, kernel="tcgen05"):
+def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False):
     caches, table = _cache_case(prompts, length, dev, 4)
     start = torch.arange(prompts + 1, dtype=torch.int32, device=dev) * length
     pos0 = torch.zeros(prompts, dtype=torch.int32, device=dev)
     qkv = torch.randn(prompts * length, 3 * H * D, device=dev).to(torch.bfloat16)      # as the fused projection leaves them
     q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
-    new = {"k_new": k, "v_new": v} if kernel == "tcgen05" else {}
+    new = {"k_new": k, "v_new": v, "store_new": store} if kernel == "tcgen05" else {}
     run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None, kernel=kernel, **new)
     return run, {"bytes": prompts * length * H * D * 6, "flops": prompts * 4 * (length * (length + 1) // 2) * H * D}
 
 
 def build(name, device="cuda:0"):
-    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> (page streaming) | attn_decode_rows_b<batch> | attn_prefill | attn_prefill_mma |
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> (page streaming) | attn_decode_rows_b<batch> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
     attn_prefill_long (one prompt of 4,096 tokens)"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
@@ -84,6 +84,8 @@ def build(name, device="cuda:0"):
         return _decode_case(int(name[len("attn_decode_b"):]), 768, device)
     if name == "attn_prefill":
         return _prefill_case(2, 1024, device)
+    if name == "attn_prefill_store":
+        return _prefill_case(2, 1024, device, store=True)
     if name == "attn_prefill_mma":
         return _prefill_case(2, 1024, device, kernel="mma")
     if name == "attn_prefill_long":

@@ -45,7 +45,7 @@ _SIGNATURES = {
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void],
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
-        "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
+        "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                         + [_c_int] * 6 + [_c_float, _c_void, _c_void],
         "dd_attention_decode_pages_supported": [_c_int] * 5,
         "dd_attention_decode_pages_splits": [_c_int] * 5,
@@ -397,14 +397,19 @@ def attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, 
         library("tensor").dd_attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, BF16))
 
 
+ATTENTION_PREFILL_TCGEN05_KEY_BLOCK = 128       # keys per block of the tcgen05 prompt attention
+
+
 def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, scale, window=None, out=None, kernel="mma",
-                      k_new=None, v_new=None):
+                      k_new=None, v_new=None, store_new=False):
     """Tensor-core attention for runs of consecutive tokens (prompt portions; a decoded token is a run of one)
     over a bfloat16 cache. entry_start: int32 [E+1], entry_pos0: int32 [E]. kernel: 'mma' (mma.sync tiles of 64
     queries, see attention_prefill_supported) or 'tcgen05' (tiles of 128 queries with TMA and TMEM accumulators,
     see attention_prefill_tcgen05_supported). The cache must hold this step's keys and values already; k_new/v_new
     (row views of the buffer q lives in, the same values) let the tcgen05 kernel read the key blocks that lie wholly
-    in this step from there, in one piece per block instead of page by page."""
+    in this step from there, in one piece per block instead of page by page. store_new: the tcgen05 kernel writes
+    k_new/v_new into the cache itself (no kv_store before it); only for steps whose entries all start at a position
+    that is a multiple of ATTENTION_PREFILL_TCGEN05_KEY_BLOCK (an entry that does not sets error bit 2)."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n, n_entries = q.shape[0], entry_pos0.numel()
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
@@ -419,7 +424,9 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
             or v_new.stride(1) != 1 or k_new.dtype != q.dtype or v_new.dtype != q.dtype
             or k_new.shape != (n, kv_heads * head_dim) or v_new.shape != k_new.shape)):
         raise KernelError("attention_prefill: k_new and v_new come together, as row views like q, for the tcgen05 kernel")
-    new_rows = (_ptr(k_new, "k_new"), _ptr(v_new, "v_new")) if kernel == "tcgen05" else ()
+    if store_new and k_new is None:
+        raise KernelError("attention_prefill: store_new needs k_new and v_new")
+    new_rows = (_ptr(k_new, "k_new"), _ptr(v_new, "v_new"), int(bool(store_new))) if kernel == "tcgen05" else ()
     _call(library("tensor"), "dd_attention_prefill" + ("_tcgen05" if kernel == "tcgen05" else ""), _ptr(q, "q"), q.stride(0), *new_rows,
           _ptr(cache, "cache"),
           _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,

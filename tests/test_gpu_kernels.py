@@ -85,7 +85,8 @@ def test_gemm_simt(K, dtype, shape):
     assert torch.equal(alone[0], K.gemm_simt(a, w, bias)[3 if M > 3 else 0])
 
 
-def paged_case(K, dtype, n_heads, kv_heads, d, page, lengths, new, window, n_splits, seed=0, poison=True, spike=None):
+def paged_case(K, dtype, n_heads, kv_heads, d, page, lengths, new, window, n_splits, seed=0, poison=True, spike=None,
+               store=True):
     """Requests with `lengths` tokens of which the last `new` are this step's queries."""
     g = torch.Generator().manual_seed(seed)
     max_blocks = (max(lengths) + page - 1) // page + 1
@@ -132,7 +133,8 @@ def paged_case(K, dtype, n_heads, kv_heads, d, page, lengths, new, window, n_spl
     ent = torch.tensor(ent, dtype=torch.int32, device=DEV)
     pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
     table = table.to(DEV)
-    K.kv_store(kv_, vv_, ent, pos, table, cache)
+    if store:
+        K.kv_store(kv_, vv_, ent, pos, table, cache)
     return dict(q=qv, cache=cache, ent=ent, pos=pos, table=table, ref=torch.cat(refs), scale=scale, packed=packed)
 
 
@@ -283,6 +285,49 @@ def test_attention_prefill_tcgen05(K, heads, kv_heads, page, window):
                                  kernel="tcgen05", k_new=packed[:, hd:hd + kd], v_new=packed[:, hd + kd:])
     assert K.read_error_flag(DEV) == 0
     assert torch.equal(direct, out)
+
+
+@pytest.mark.parametrize("heads,kv_heads,page", [(5, 5, 16), (6, 2, 128), (4, 1, 8)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_prefill_tcgen05_writes_the_cache(K, heads, kv_heads, page, window):
+    """With store_new the kernel puts the step's keys and values into the pages itself: the same result, and the
+    same live cache rows bit for bit, as after kv_store. Every portion starts at a multiple of 128 keys, ends anywhere."""
+    K.library("tensor")
+    lengths, new = [150, 128 + 3, 256 + 300, 1, 384 + 129, 640], [150, 3, 300, 1, 129, 256]
+    kw = dict(lengths=lengths, new=new, window=window, n_splits=1, spike=3 if window is None else None)
+    c = paged_case(K, torch.bfloat16, heads, kv_heads, 64, page, store=False, **kw)
+    stored = paged_case(K, torch.bfloat16, heads, kv_heads, 64, page, **kw)
+    assert not torch.equal(c["cache"].view(torch.int16), stored["cache"].view(torch.int16))
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    entry_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    entry_pos0 = torch.tensor([L - n for L, n in zip(lengths, new)], dtype=torch.int32, device=DEV)
+    hd, kd = heads * 64, kv_heads * 64
+    packed = c["packed"]
+    out = K.attention_prefill(packed[:, :hd], c["cache"], entry_start, entry_pos0, c["table"], heads, c["scale"], window,
+                              kernel="tcgen05", k_new=packed[:, hd:hd + kd], v_new=packed[:, hd + kd:], store_new=True)
+    assert K.read_error_flag(DEV) == 0
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    # slot by slot up to each request's length; what lies beyond in a request's last page is never read
+    live = torch.zeros(c["cache"].shape[0], page, dtype=torch.bool)
+    for e, L in enumerate(lengths):
+        for pos in range(L):
+            live[int(c["table"][e, pos // page]), pos % page] = True
+    live = live.to(DEV)[:, None, None, :, None]
+    ours, theirs = c["cache"].view(torch.int16), stored["cache"].view(torch.int16)
+    assert torch.equal(torch.where(live, ours, 0), torch.where(live, theirs, 0))
+    untouched = ~live.flatten(1).any(1)                      # pages of no request
+    assert torch.equal(ours[untouched], theirs[untouched])
+    # a portion that starts inside a key block is refused on the device: error bit 2 and nothing written
+    before = c["cache"].clone()
+    K.attention_prefill(packed[:, :hd], c["cache"], entry_start, entry_pos0 + 1, c["table"], heads, c["scale"], window,
+                        kernel="tcgen05", k_new=packed[:, hd:hd + kd], v_new=packed[:, hd + kd:], store_new=True)
+    assert K.read_error_flag(DEV) & 2
+    assert torch.equal(c["cache"].view(torch.int16), before.view(torch.int16))
+    with pytest.raises(K.KernelError, match="store_new"):
+        K.attention_prefill(packed[:, :hd], c["cache"], entry_start, entry_pos0, c["table"], heads, c["scale"], window,
+                            kernel="tcgen05", store_new=True)
 
 
 def test_attention_rejects_bad_sizes(K):

@@ -51,6 +51,31 @@ def test_xl_layer_sizes(xl, dtype):
     assert engine.cache.used_tokens == 0
 
 
+def test_xl_portions_on_key_block_boundaries(xl):
+    """Portions that start at positions 0 and 128: there the prompt attention kernel writes the cache itself (no
+    separate cache-write kernel). A third portion starts inside a key block and reads what the first two left; the
+    decoded tokens read all of it. The cache starts out poisoned."""
+    from damendaemon_b200.engine import Engine, StepEntry
+    folder, tokens, rows, want, moved = xl
+    engine = Engine(folder, dtype="bfloat16", kv_tokens=384, page_size=16, max_requests=2, use_graph=True)
+    for g in engine.cache.groups:
+        g.arena.fill_(float("nan"))
+    got = {}
+    for lo, hi in [(0, 128), (128, 300), (300, 321)]:
+        asked = [r for r in rows if lo <= r < hi]
+        out = engine.step([StepEntry("r", tokens[lo:hi], [r - lo for r in asked])]).cpu()
+        for r, row in zip(asked, out):
+            got[r] = row
+    for p in range(321, 331):
+        got[p] = engine.step([StepEntry("r", [tokens[p]], [0])]).cpu()[0].clone()
+    tol = 3.0 * moved + 2e-3
+    for i, r in enumerate(rows):
+        err = (got[r] - want[i]).abs().max().item()
+        assert err < tol, f"position {r} differs by {err:.3e} (allowed {tol:.3e})"
+    engine.finish("r")
+    assert engine.cache.used_tokens == 0
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_xl_decode_of_eight_requests(xl, use_graph):
     """Eight requests of different lengths decoded together, in bfloat16: 8 x 25 heads is where the engine switches to
