@@ -68,12 +68,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const __grid_constant__ CUtensorMap map_k_new, const __grid_constant__ CUtensorMap map_v_new,
                                  const AttnParams p) {
     dd_launch_dependents();
-    // which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once.
-    int e = 0, tile = blockIdx.x, len = 0;
+    // Which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once. The heads of a
+    // tile are neighbours in launch order and an entry's tiles come last tile first: the last tile has the most key
+    // blocks to walk, and the blocks that are launched last, which decide when the kernel ends, should be short ones.
+    int e = 0, tile = blockIdx.y, len = 0;
     for (; e < p.n_entries; ++e) {
         len = p.entry_start[e + 1] - p.entry_start[e];
         const int nt = (len + BQ - 1) / BQ;
-        if (tile < nt) break;
+        if (tile < nt) {
+            tile = nt - 1 - tile;
+            break;
+        }
         tile -= nt;
     }
     if (e == p.n_entries) return;
@@ -93,7 +98,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     float* row_max = reinterpret_cast<float*>(sKV + STAGES * STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y, kh = h / (p.H / p.KH);
+    const int h = blockIdx.x, kh = h / (p.H / p.KH);
     const int q0 = tile * BQ;
     const int rows = min(BQ, len - q0);
     const int row0 = p.entry_start[e] + q0;
@@ -472,7 +477,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
                        head_dim, page_size, n_heads, n_kv_heads);
     if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
         return dd_fail("dd_attention_prefill_tcgen05: rows must be 16-byte aligned");
-    if (n_heads > 65535) return dd_fail("dd_attention_prefill_tcgen05: too many heads");
+    if (dd_ceil_div(n_tokens, BQ) + n_entries > 65535) return dd_fail("dd_attention_prefill_tcgen05: too many tokens for one launch");
     if (!(scale > 0.f)) return dd_fail("dd_attention_prefill_tcgen05: the score scale must be positive");
     static bool configured = false;
     if (!configured) {
@@ -500,7 +505,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.new_rows = k_new != nullptr;
     p.store_new = store_new != 0;
     // an upper bound of the number of 128-row tiles; blocks beyond the real count return at once
-    dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, n_heads);
+    dim3 grid(n_heads, dd_ceil_div(n_tokens, BQ) + n_entries);
     dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, map_k_new, map_v_new, p);
     return dd_check_launch("dd_attention_prefill_tcgen05");
 }
