@@ -30,13 +30,15 @@
 #include <math_constants.h>
 
 namespace {
-constexpr int BQ = 128, BKV = 128, D = 64, THREADS = 64 + 256, STAGES = 4;
+constexpr int BQ = 128, TILES = 2, BKV = 128, D = 64, THREADS = 64 + TILES * 128, STAGES = 4;
 constexpr int TILE_BYTES = BKV * D * 2;             // one 128 x 64 bf16 tile: 16 KB
+constexpr int Q_BYTES = TILES * TILE_BYTES;         // the two query tiles, one after the other
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // keys, then values
-constexpr int EXCHANGE_BYTES = 6 * BQ * 4;           // row maxima of the two halves (two buffers), then the two row sums
-constexpr int SMEM_BYTES = TILE_BYTES + STAGES * STAGE_BYTES + 1024 + 256 + EXCHANGE_BYTES;
-constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O: 64 columns
-constexpr int S_COL = 0, O_COL = 256;
+constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;                      // per tile: scores 128 columns, P 64, output 64
+__host__ __device__ constexpr int s_col(int t) { return t * BKV; }
+__host__ __device__ constexpr int p_col(int t) { return TILES * BKV + t * (BKV / 2); }
+__host__ __device__ constexpr int o_col(int t) { return TILES * BKV + TILES * (BKV / 2) + t * D; }
 
 struct AttnParams {
     const int* entry_start;
@@ -68,44 +70,52 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const __grid_constant__ CUtensorMap map_k_new, const __grid_constant__ CUtensorMap map_v_new,
                                  const AttnParams p) {
     dd_launch_dependents();
-    // Which 128-row tile of which entry is this block's? Blocks beyond the real count leave at once. The heads of a
-    // tile are neighbours in launch order and an entry's tiles come last tile first: the last tile has the most key
-    // blocks to walk, and the blocks that are launched last, which decide when the kernel ends, should be short ones.
-    int e = 0, tile = blockIdx.y, len = 0;
+    // Which pair of 128-row tiles of which entry is this block's? Blocks beyond the real count leave at once. The
+    // heads of a pair are neighbours in launch order and an entry's pairs come last pair first: the last one has the
+    // most key blocks to walk, and the blocks that are launched last, which decide when the kernel ends, should be
+    // short ones.
+    int e = 0, pair = blockIdx.y, len = 0;
     for (; e < p.n_entries; ++e) {
         len = p.entry_start[e + 1] - p.entry_start[e];
-        const int nt = (len + BQ - 1) / BQ;
-        if (tile < nt) {
-            tile = nt - 1 - tile;
+        const int np = (len + TILES * BQ - 1) / (TILES * BQ);
+        if (pair < np) {
+            pair = np - 1 - pair;
             break;
         }
-        tile -= nt;
+        pair -= np;
     }
     if (e == p.n_entries) return;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sQ = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sKV = sQ + TILE_BYTES;
+    uint8_t* sKV = sQ + Q_BYTES;
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(sKV + STAGES * STAGE_BYTES);
     uint64_t* kv_empty = kv_full + STAGES;
     uint64_t* q_full = kv_empty + STAGES;
-    uint64_t* s_full = q_full + 1;        // [2]
-    uint64_t* p_ready = s_full + 2;       // [2]
-    uint64_t* o_full = p_ready + 2;       // [0]: the P.V product of a block has been added to the output (one phase per block)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    uint64_t* s_full = q_full + 1;        // [tile]: the scores of the tile's next key block are in tensor memory
+    uint64_t* s_free = s_full + TILES;    // [tile]: the softmax warps hold them in registers, the columns may be overwritten
+    uint64_t* p_ready = s_free + TILES;   // [tile]: P of the block is in tensor memory (and dead value rows are zeros)
+    uint64_t* o_full = p_ready + TILES;   // [tile]: the P.V product of the block has been added to the tile's output
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + TILES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* softmax_abort = abort_flag + 1;          // written by softmax threads only, read after their barrier
-    float* row_max = reinterpret_cast<float*>(sKV + STAGES * STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, kh = h / (p.H / p.KH);
-    const int q0 = tile * BQ;
-    const int rows = min(BQ, len - q0);
+    const int q0 = pair * TILES * BQ;
+    const int rows_all = min(TILES * BQ, len - q0);
+    const int n_tiles = rows_all > BQ ? 2 : 1;
     const int row0 = p.entry_start[e] + q0;
-    const int pos_first = p.entry_pos0[e] + q0, pos_last = pos_first + rows - 1;
-    const int kv_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int kb_first = kv_lo / BKV * BKV;
+    const int pos0 = p.entry_pos0[e];
+    const int pos_first = pos0 + q0, pos_last = pos_first + rows_all - 1;       // of the pair
+    // first and last position of tile t, the first key its window lets it see, and the key blocks it takes part in
+    // (counted from the pair's first): the upper tile walks on where the lower one has met its diagonal
+    auto tile_first = [&](int t) { return pos_first + t * BQ; };
+    auto tile_last = [&](int t) { return min(pos_first + t * BQ + BQ - 1, pos_last); };
+    auto tile_lo = [&](int t) { return p.window > 0 ? max(0, tile_first(t) - p.window + 1) : 0; };
+    const int kb_first = tile_lo(0) / BKV * BKV;
     const int n_blocks = (pos_last - kb_first) / BKV + 1;
+    auto block_first = [&](int t) { return (tile_lo(t) / BKV * BKV - kb_first) / BKV; };
+    auto block_last = [&](int t) { return (tile_last(t) - kb_first) / BKV; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -113,13 +123,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc::mbar_init(&kv_empty[s], 1);
         }
         tc::mbar_init(q_full, 1);
-        for (int b = 0; b < 2; ++b) {
-            tc::mbar_init(&s_full[b], 1);
-            tc::mbar_init(&p_ready[b], 8);        // one arrival per softmax warp
-            tc::mbar_init(&o_full[b], 1);
+        for (int t = 0; t < TILES; ++t) {
+            tc::mbar_init(&s_full[t], 1);
+            tc::mbar_init(&s_free[t], 4);         // one arrival per softmax warp of the tile
+            tc::mbar_init(&p_ready[t], 4);
+            tc::mbar_init(&o_full[t], 1);
         }
         *abort_flag = 0;
-        *softmax_abort = 0;
         tc::fence_barrier_init();
         tc::fence_proxy_async();
         tc::prefetch_tensormap(&map_q);
@@ -143,12 +153,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (warp == 0) {
         // ---- TMA ----
         if (lane == 0) {
-            tc::mbar_expect_tx(q_full, TILE_BYTES);
+            tc::mbar_expect_tx(q_full, Q_BYTES);
             tc::tma_load_2d(sQ, &map_q, h * D, row0, q_full);       // rows past the last token read as zeros
         }
         const int pages_per_block = BKV / p.P;
         const int* bt = p.block_table + (size_t)e * p.max_blocks;
         const uint32_t page_bytes = (uint32_t)p.P * D * 2;
+        const int kv_lo = tile_lo(0);
         // The warp holds 32 consecutive entries of the request's block table, one per lane, and the next 32 already
         // requested: a key block's pages never straddle such a window (its first entry is a multiple of the pages
         // per block, which divide 32), and no block waits for a table read of its own.
@@ -166,13 +177,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int kb = kb_first + j * BKV;
             uint8_t* k_dst = sKV + s * STAGE_BYTES;
             uint8_t* v_dst = k_dst + TILE_BYTES;
-            if (p.new_rows && kb >= pos_first - q0) {
+            if (p.new_rows && kb >= pos0) {
                 // Every key of this block is one of this step's own: they lie row after row beside the queries, so one
                 // box of 128 rows brings the keys and one the values (a box per cache page costs the TMA unit about
                 // 60 ns each, 1 us per block with pages of 16 tokens, which is what bounded whole prompts). Rows past
                 // the entry are other requests' tokens or zeros: masked by position like any key after the query.
                 if (lane == 0) {
-                    const int row = (row0 - q0) + kb - (pos_first - q0);       // the entry's first row + (key - its first position)
+                    const int row = (row0 - q0) + kb - pos0;       // the entry's first row + (key - its first position)
                     tc::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
                     tc::tma_load_2d(k_dst, &map_k_new, kh * D, row, &kv_full[s]);
                     tc::tma_load_2d(v_dst, &map_v_new, kh * D, row, &kv_full[s]);
@@ -216,21 +227,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (stamps && lane == 0 && j < 8) stamps[56 + j] = tc::global_ns();
         }
         if (p.store_new && h % (p.H / p.KH) == 0) {
-            // This tile's own keys and values are the last key block, and they lie in shared memory in the layout of
-            // the cache's tensor map: TMA writes them into the tile's pages, one box per page, while the block works on
-            // them. No block of this launch reads these cache rows: with every entry starting on a key-block boundary,
-            // the key blocks that hold this step's tokens are read from k_new/v_new. A page that the entry fills only
-            // in part receives whatever follows the entry's last token in its other slots; slots past a request's
-            // length are never read by anyone.
-            if ((pos_first - q0) % BKV != 0) {
+            // The pair's own keys and values are its last key blocks (one per tile), and they lie in shared memory in
+            // the layout of the cache's tensor map: TMA writes them into their pages, one box per page, while the block
+            // works on them. No block of this launch reads these cache rows: with every entry starting on a key-block
+            // boundary, the key blocks that hold this step's tokens are read from k_new/v_new. A page that the entry
+            // fills only in part receives whatever follows the entry's last token in its other slots; slots past a
+            // request's length are never read by anyone.
+            if (pos0 % BKV != 0) {
                 if (lane == 0) atomicOr(p.error_flag, 2);        // the caller broke the rule: nothing is written
             } else {
-                const int j = n_blocks - 1, s = j % STAGES;
-                if (tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) {
+                for (int j = n_blocks - n_tiles; j < n_blocks; ++j) {
+                    const int s = j % STAGES, kb = kb_first + j * BKV;
+                    if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) break;
                     if (lane < 2 * pages_per_block) {
                         const int slot = lane < pages_per_block ? lane : lane - pages_per_block;
                         const bool values = lane >= pages_per_block;
-                        const int key0 = pos_first + slot * p.P;
+                        const int key0 = kb + slot * p.P;
                         if (key0 <= pos_last) {
                             const int page = bt[key0 / p.P];
                             if (page < 0 || page >= p.n_pages) atomicOr(p.error_flag, 2);
@@ -239,9 +251,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                                  sKV + s * STAGE_BYTES + (values ? TILE_BYTES : 0) + slot * page_bytes);
                         }
                     }
-                    tc::bulk_commit();
-                    tc::bulk_wait_all();         // shared memory has been read and the cache written before the block leaves
                 }
+                tc::bulk_commit();
+                tc::bulk_wait_all();         // shared memory has been read and the cache written before the block leaves
             }
         }
     } else if (warp == 1) {
@@ -250,119 +262,156 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             constexpr uint32_t idesc_s = tc::idesc_bf16_f32(BQ, BKV);
             constexpr uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(BQ, D);
             const uint32_t q_addr = tc::smem_u32(sQ);
+            int first[TILES], last[TILES], scored[TILES], added[TILES];
+#pragma unroll
+            for (int t = 0; t < TILES; ++t) {
+                first[t] = block_first(t);
+                last[t] = t < n_tiles ? block_last(t) : -1;
+                scored[t] = added[t] = 0;
+            }
             bool ok = tc::mbar_wait(q_full, 0, abort_flag);
             tc::fence_after_sync();
+            // S_t = Q_t K_j^T for the tiles that take part in key block j, as soon as a tile's softmax warps have taken
+            // its previous scores into registers
             auto issue_scores = [&](int j) {
                 const int s = j % STAGES;
                 if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) { ok = false; return; }
-                tc::fence_after_sync();
                 const uint32_t k_addr = tc::smem_u32(sKV + s * STAGE_BYTES);
-                const uint32_t tmem_s = tmem_base + S_COL + (j & 1) * BKV;
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k)
-                    tc::mma_bf16(tmem_s, tc::smem_desc_sw128(q_addr + k * 32), tc::smem_desc_sw128(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
-                tc::mma_commit(&s_full[j & 1]);
+                for (int t = 0; t < TILES; ++t) {
+                    if (j < first[t] || j > last[t]) continue;
+                    if (scored[t] > 0 && !tc::mbar_wait(&s_free[t], (scored[t] - 1) & 1, abort_flag)) { ok = false; return; }
+                    tc::fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k)
+                        tc::mma_bf16(tmem_base + s_col(t), tc::smem_desc_sw128(q_addr + t * TILE_BYTES + k * 32),
+                                     tc::smem_desc_sw128(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
+                    tc::mma_commit(&s_full[t]);
+                    ++scored[t];
+                }
             };
             if (ok) issue_scores(0);
-            if (ok && n_blocks > 1) issue_scores(1);
             for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j % STAGES, b = j & 1;
-                if (!tc::mbar_wait(&p_ready[b], (j >> 1) & 1, abort_flag)) break;
-                tc::fence_after_sync();
-                if (stamps && j < 8) stamps[40 + 2 * j] = tc::global_ns();
+                if (j + 1 < n_blocks) issue_scores(j + 1);
+                if (!ok) break;
+                // O_t += P_t V_j, for each tile as soon as its P is there, whichever comes first
+                const int s = j % STAGES;
                 const uint32_t v_addr = tc::smem_u32(sKV + s * STAGE_BYTES + TILE_BYTES);
-                const uint32_t tmem_p = tmem_base + S_COL + b * BKV;     // P_j lies over the first 64 columns of S_j
-                const uint32_t tmem_o = tmem_base + O_COL;          // the output accumulates in TMEM over all blocks
+                uint32_t pending = 0;
 #pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                    tc::mma_bf16_a_tmem(tmem_o, tmem_p + k * 8, tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o,
-                                        (j > 0 || k > 0) ? 1u : 0u);
-                tc::mma_commit(&o_full[0]);
-                tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
-                if (j + 2 < n_blocks) issue_scores(j + 2);   // its score buffer is free: P_j exists
+                for (int t = 0; t < TILES; ++t)
+                    if (j >= first[t] && j <= last[t]) pending |= 1u << t;
+                const unsigned long long start = tc::global_ns();
+                uint32_t spins = 0;
+                while (pending && ok) {
+#pragma unroll
+                    for (int t = 0; t < TILES; ++t) {
+                        if (!(pending & (1u << t)) || !tc::mbar_try_wait(&p_ready[t], added[t] & 1)) continue;
+                        tc::fence_after_sync();
+                        if (stamps && j < 8 && t == 0) stamps[40 + 2 * j] = tc::global_ns();
+#pragma unroll
+                        for (int k = 0; k < BKV / 16; ++k)
+                            tc::mma_bf16_a_tmem(tmem_base + o_col(t), tmem_base + p_col(t) + k * 8,
+                                                tc::smem_desc_sw128_mn(v_addr + k * 16 * D * 2, 1024), idesc_o,
+                                                (added[t] > 0 || k > 0) ? 1u : 0u);
+                        tc::mma_commit(&o_full[t]);
+                        ++added[t];
+                        pending &= ~(1u << t);
+                    }
+                    if (pending && (++spins & 0x3ff) == 0 && (*abort_flag || tc::global_ns() - start > tc::WAIT_LIMIT_NS)) {
+                        *abort_flag = 1;
+                        ok = false;
+                    }
+                }
+                if (ok) tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
                 if (stamps && j < 8) stamps[41 + 2 * j] = tc::global_ns();
             }
         }
-    } else {
-        // ---- softmax and output: two threads per query row (its TMEM lane), one for each half of a block's keys ----
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+    } else if (((warp - 2) >> 2) < n_tiles) {
+        // ---- softmax and output: four warps per tile, a thread owns one query row (its TMEM lane) ----
+        const int t = (warp - 2) >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;
-        const int qpos = pos_first + r;
+        const int t_first = tile_first(t), rows = tile_last(t) - t_first + 1;
+        const int qpos = t_first + r;
         const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+        const int j_first = block_first(t), j_last = block_last(t);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        constexpr int HALF = BKV / 2, DH = D / 2;          // keys and output dimensions of one thread
         // m: the maximum the row's exponentials, sum and output are relative to. It follows the true running maximum only
         // when that has moved ahead by more than 8 (a factor of 256, harmless in float32 and bfloat16): only then is the
-        // output row in TMEM rescaled, which is rare after the first blocks. l: this thread's half of the row's sum.
+        // output row in TMEM rescaled, which is rare after the first blocks. l: the row's sum.
         float m = -CUDART_INF_F, l = 0.f;
-        for (int j = 0; j < n_blocks; ++j) {
-            const int b = j & 1, kb = kb_first + j * BKV, k0 = kb + half * HALF;
-            const bool have = tc::mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag);
-            if (!have) *softmax_abort = 1;
+        bool alive = true;
+        for (int j = j_first, c = 0; j <= j_last && alive; ++j, ++c) {
+            const int kb = kb_first + j * BKV;
+            alive = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[t], c & 1, abort_flag));
+            if (!alive) break;
             tc::fence_after_sync();
-            const bool stamp = stamps && threadIdx.x == 64 && j < 8;
-            if (stamp) stamps[8 + 4 * j] = tc::global_ns();
-            const uint32_t s_addr = lane_addr + S_COL + b * BKV + half * HALF;
-            // this thread's 64 scores of the block: two loads in flight, one wait
-            uint32_t sv[HALF];
-            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            if (have) {
+            const bool stamp = stamps && threadIdx.x == 64 && c < 8;
+            if (stamp) stamps[8 + 4 * c] = tc::global_ns();
+            // the row's 128 scores of the block into registers: four loads in flight, one wait; then the columns are free
+            uint32_t sv[BKV];
 #pragma unroll
-                for (int c0 = 0; c0 < HALF; c0 += 32) tc::tmem_ld_x32(s_addr + c0, sv + c0);
-                tc::tmem_ld_wait();
-                if (k0 + HALF - 1 > qpos || k0 < qlo) {
+            for (int c0 = 0; c0 < BKV; c0 += 32) tc::tmem_ld_x32(lane_addr + s_col(t) + c0, sv + c0);
+            tc::tmem_ld_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&s_free[t]);
+            if (kb + BKV - 1 > qpos || kb < qlo) {
 #pragma unroll
-                    for (int i = 0; i < HALF; ++i)
-                        if (k0 + i > qpos || k0 + i < qlo) sv[i] = 0xff800000u;      // -inf: replaced, whatever was there
-                }
-#pragma unroll
-                for (int i = 0; i < HALF; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                for (int i = 0; i < BKV; ++i)
+                    if (kb + i > qpos || kb + i < qlo) sv[i] = 0xff800000u;      // -inf: replaced, whatever was there
             }
-            // the two halves of a row exchange their maxima (buffers alternate, so one barrier per block is enough)
-            float* xchg = row_max + (j & 1) * 2 * BQ;
-            xchg[half * BQ + r] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            asm volatile("bar.sync 2, 256;" ::: "memory");
-            if (*softmax_abort) break;                     // the same decision in all eight warps
-            const float mx = fmaxf(xchg[r], xchg[BQ + r]);
-            if (stamp) stamps[9 + 4 * j] = tc::global_ns();
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (stamp) stamps[9 + 4 * c] = tc::global_ns();
             const float m_true = fmaxf(m, mx * p.scale_log2e);     // the scale is positive
             const bool move = m_true > m + 8.f || (m == -CUDART_INF_F && m_true != -CUDART_INF_F);
             const float alpha = move ? exp2_approx(m - m_true) : 1.f;      // 0 from -inf
             if (move) m = m_true;
             const float msub = m == -CUDART_INF_F ? 0.f : m;
-            if (j > 0 && __any_sync(0xffffffffu, move)) {
-                // rescale this thread's 32 output dimensions in TMEM: P_{j-1} V_{j-1} must have been added first
-                if (!tc::mbar_wait(&o_full[0], (j - 1) & 1, abort_flag)) *softmax_abort = 1;
-                else {
-                    tc::fence_after_sync();
-                    uint32_t v[DH];
-                    tc::tmem_ld_x32(lane_addr + O_COL + half * DH, v);
-                    tc::tmem_ld_wait();
+            if (c > 0) {
+                // P of the block before has been read and its product added to the output: P may be overwritten, the
+                // output rescaled
+                alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (c - 1) & 1, abort_flag));
+                if (!alive) break;
+                tc::fence_after_sync();
+                if (__any_sync(0xffffffffu, move)) {
 #pragma unroll
-                    for (int i = 0; i < DH; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tc::tmem_st_x32(lane_addr + O_COL + half * DH, v);
-                    tc::tmem_st_wait();
+                    for (int d0 = 0; d0 < D; d0 += 16) {          // in small pieces: the scores fill the registers
+                        uint32_t v[16];
+                        tc::tmem_ld_x16(lane_addr + o_col(t) + d0, v);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tc::tmem_st_x16(lane_addr + o_col(t) + d0, v);
+                    }
                 }
             }
-            // exponentials (a masked score gives exactly 0), their sum, and P as bfloat16 into tensor memory, over the
-            // first 64 columns of this block's scores (every thread of the row has its scores in registers since the
-            // exchange above): two consecutive keys per column, this thread's 64 keys in columns 32*half .. 32*half+31
+            // exponentials (a masked score gives exactly 0), their sum, and P as bfloat16 into tensor memory: two
+            // consecutive keys per column
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[HALF / 2];
 #pragma unroll
-            for (int i = 0; i < HALF / 2; ++i) {
-                const float p0 = exp2_approx(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2e, -msub));
-                const float p1 = exp2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2e, -msub));
-                sum4[i & 3] += p0 + p1;
-                packed[i] = pack_bf16(p0, p1);
+            for (int c0 = 0; c0 < BKV; c0 += 32) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = exp2_approx(fmaf(__uint_as_float(sv[c0 + 2 * i]), p.scale_log2e, -msub));
+                    const float p1 = exp2_approx(fmaf(__uint_as_float(sv[c0 + 2 * i + 1]), p.scale_log2e, -msub));
+                    sum4[i & 3] += p0 + p1;
+                    packed[i] = pack_bf16(p0, p1);
+                }
+                tc::tmem_st_x16(lane_addr + p_col(t) + c0 / 2, packed);
             }
-            tc::tmem_st_x32(lane_addr + S_COL + b * BKV + half * (HALF / 2), packed);
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (kb + BKV - 1 > pos_last) {
-                // value rows of keys past the tile's last query: unwritten cache slots, to be zeros under P = 0
+                // value rows of keys past the pair's last query: unwritten cache slots, to be zeros under P = 0 (where
+                // both tiles take part in such a block both write these zeros)
                 const int s = j % STAGES;
-                if (!tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) *softmax_abort = 1;
-                else if (half == 0 && kb + r > pos_last) {
+                alive = __all_sync(0xffffffffu, tc::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag));
+                if (!alive) break;
+                if (kb + r > pos_last) {
                     uint4* z = reinterpret_cast<uint4*>(sKV + s * STAGE_BYTES + TILE_BYTES + r * 128);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) z[i] = make_uint4(0, 0, 0, 0);
@@ -372,31 +421,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc::fence_proxy_async();          // the zeroed value rows to the proxy the MMA reads through
             tc::fence_before_sync();          // this thread's TMEM reads and writes are done
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&p_ready[b]);
-            if (stamp) stamps[10 + 4 * j] = tc::global_ns();
-            if (stamp) stamps[11 + 4 * j] = tc::global_ns();
+            if (lane == 0) tc::mbar_arrive(&p_ready[t]);
+            if (stamp) stamps[10 + 4 * c] = tc::global_ns();
         }
-        // the output row after the last block's P.V, and the two halves of the row sum
-        {
-            if (!*softmax_abort && !tc::mbar_wait(&o_full[0], (n_blocks - 1) & 1, abort_flag)) *softmax_abort = 1;
-            row_max[4 * BQ + half * BQ + r] = l;
-            asm volatile("bar.sync 2, 256;" ::: "memory");
-            if (!*softmax_abort) {
-                tc::fence_after_sync();
-                uint32_t v[DH];
-                tc::tmem_ld_x32(lane_addr + O_COL + half * DH, v);
+        // the output row after the last block's P.V
+        if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (j_last - j_first) & 1, abort_flag));
+        if (alive) {
+            tc::fence_after_sync();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + t * BQ + r) * p.out_stride + (size_t)h * D;
+#pragma unroll
+            for (int d0 = 0; d0 < D; d0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld_x32(lane_addr + o_col(t) + d0, v);
                 tc::tmem_ld_wait();
                 if (r < rows) {
-                    const float sum = row_max[4 * BQ + r] + row_max[5 * BQ + r];
-                    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-                    __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * D + half * DH;
 #pragma unroll
-                    for (int c = 0; c < DH; c += 8) {
+                    for (int c = 0; c < 32; c += 8) {
                         float f[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c + i]) * inv;
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
-                                                                          pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                        *reinterpret_cast<uint4*>(dst + d0 + c) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
+                                                                               pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
                     }
                 }
             }
@@ -477,7 +523,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
                        head_dim, page_size, n_heads, n_kv_heads);
     if (q_stride % 8 || out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
         return dd_fail("dd_attention_prefill_tcgen05: rows must be 16-byte aligned");
-    if (dd_ceil_div(n_tokens, BQ) + n_entries > 65535) return dd_fail("dd_attention_prefill_tcgen05: too many tokens for one launch");
+    if (dd_ceil_div(n_tokens, TILES * BQ) + n_entries > 65535) return dd_fail("dd_attention_prefill_tcgen05: too many tokens for one launch");
     if (!(scale > 0.f)) return dd_fail("dd_attention_prefill_tcgen05: the score scale must be positive");
     static bool configured = false;
     if (!configured) {
@@ -489,7 +535,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
         return dd_fail("dd_attention_prefill_tcgen05: k_new and v_new come together, 16-byte aligned");
     if (store_new && !k_new) return dd_fail("dd_attention_prefill_tcgen05: store_new needs k_new and v_new");
     CUtensorMap map_q, map_kv, map_k_new, map_v_new;
-    if (int e = make_map(&map_q, q, (unsigned long long)n_tokens, n_heads * D, q_stride, BQ, "the queries")) return e;
+    if (int e = make_map(&map_q, q, (unsigned long long)n_tokens, n_heads * D, q_stride, TILES * BQ, "the queries")) return e;
     // this step's keys and values as rows of the same stride as the queries (the fused projection's output), or the
     // queries again as a stand-in that is never read
     if (int e = make_map(&map_k_new, k_new ? k_new : q, (unsigned long long)n_tokens, (k_new ? n_kv_heads : n_heads) * D, q_stride, BKV, "this step's keys")) return e;
@@ -504,8 +550,8 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.timeline = g_timeline;
     p.new_rows = k_new != nullptr;
     p.store_new = store_new != 0;
-    // an upper bound of the number of 128-row tiles; blocks beyond the real count return at once
-    dim3 grid(n_heads, dd_ceil_div(n_tokens, BQ) + n_entries);
+    // an upper bound of the number of pairs of 128-row tiles; blocks beyond the real count return at once
+    dim3 grid(n_heads, dd_ceil_div(n_tokens, TILES * BQ) + n_entries);
     dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, map_k_new, map_v_new, p);
     return dd_check_launch("dd_attention_prefill_tcgen05");
 }
