@@ -60,6 +60,31 @@ __device__ __forceinline__ float exp2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two float32 operations in one instruction (sm_100): the softmax warps are bound by the number of instructions they
+// issue, not by any one pipe, so the scaling and the row sums work on pairs, and the maximum takes three inputs.
+__device__ __forceinline__ unsigned long long pair_of(uint32_t lo, uint32_t hi) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+    return v;
+}
+__device__ __forceinline__ void halves_of(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_pair(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add_pair(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max_of_three(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -363,7 +388,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+            for (int i = 0; i < BKV; i += 2)
+                mx4[(i >> 1) & 3] = max_of_three(mx4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             if (stamp) stamps[9 + 4 * c] = tc::global_ns();
             const float m_true = fmaxf(m, mx * p.scale_log2e);     // the scale is positive
@@ -391,18 +417,27 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             // exponentials (a masked score gives exactly 0), their sum, and P as bfloat16 into tensor memory: two
             // consecutive keys per column
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const unsigned long long scale2 = pair_of(__float_as_uint(p.scale_log2e), __float_as_uint(p.scale_log2e));
+            const unsigned long long shift2 = pair_of(__float_as_uint(-msub), __float_as_uint(-msub));
+            unsigned long long sums[4] = {0ull, 0ull, 0ull, 0ull};           // pairs of float32 zeros
 #pragma unroll
             for (int c0 = 0; c0 < BKV; c0 += 32) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(sv[c0 + 2 * i]), p.scale_log2e, -msub));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(sv[c0 + 2 * i + 1]), p.scale_log2e, -msub));
-                    sum4[i & 3] += p0 + p1;
+                    float x0, x1;
+                    halves_of(fma_pair(pair_of(sv[c0 + 2 * i], sv[c0 + 2 * i + 1]), scale2, shift2), x0, x1);
+                    const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+                    sums[i & 3] = add_pair(sums[i & 3], pair_of(__float_as_uint(p0), __float_as_uint(p1)));
                     packed[i] = pack_bf16(p0, p1);
                 }
                 tc::tmem_st_x16(lane_addr + p_col(t) + c0 / 2, packed);
+            }
+            float sum4[4];
+            {
+                float lo, hi;
+                halves_of(add_pair(add_pair(sums[0], sums[1]), add_pair(sums[2], sums[3])), lo, hi);
+                sum4[0] = lo; sum4[1] = hi; sum4[2] = 0.f; sum4[3] = 0.f;
             }
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (kb + BKV - 1 > pos_last) {
@@ -423,6 +458,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&p_ready[t]);
             if (stamp) stamps[10 + 4 * c] = tc::global_ns();
+            if (stamps && threadIdx.x == 64 + BQ && c < 8) stamps[11 + 4 * c] = tc::global_ns();
         }
         // the output row after the last block's P.V
         if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (j_last - j_first) & 1, abort_flag));
@@ -491,8 +527,9 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long rows, int co
 }  // namespace
 
 // Debugging aid: a device buffer of 64 time stamps (ns) per block of the next launches, null switches it off:
-// 0 start, 1 inputs ready; for the first eight key blocks j: 8+4j scores there, 9+4j maximum known, 10+4j P handed
-// over, 11+4j output row updated (thread 64); 40+2j P seen by the MMA thread, 41+2j its MMAs issued; 56+j loads issued.
+// 0 start, 1 inputs ready; for the first eight key blocks j of the lower tile: 8+4j scores there, 9+4j maximum known,
+// 10+4j P handed over (thread 64), 11+4j P of the upper tile's j-th block handed over; 40+2j the lower tile's P seen by
+// the MMA thread, 41+2j the block's P.V products issued; 56+j loads issued.
 DD_API void dd_attention_prefill_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
 
 // Head size 64, pages of 8, 16, 32, 64 or 128 tokens (a page is one TMA box inside a 128-key block).
