@@ -153,7 +153,9 @@ def decode_end_to_end(runtime, batch, warmup, steps, vocab):
     from damendaemon_b200.engine.scheduler import Request, Scheduler
     scheduler = Scheduler(runtime.engine, token_budget=4096)
     for i in range(batch):
-        scheduler.submit(Request(random_ids(PROMPT, vocab, 100 + i), max_tokens=warmup + steps + 1, ignore_eos=True))
+        # a few tokens beyond the timed steps: no request ends inside them, so the scheduler keeps one step in flight
+        # at both ends of the timed region, which then holds `steps` forward passes launched and waited for
+        scheduler.submit(Request(random_ids(PROMPT, vocab, 100 + i), max_tokens=warmup + steps + 4, ignore_eos=True))
     while scheduler.waiting or scheduler.prefilling:
         scheduler.step()
     for _ in range(warmup):
@@ -297,8 +299,8 @@ def main():
         return 0
     if args.warmup < 3:
         args.warmup = 3
-    if PROMPT + args.warmup + args.steps > XL["n_positions"]:
-        args.steps = XL["n_positions"] - PROMPT - args.warmup
+    if PROMPT + args.warmup + args.steps + 4 > XL["n_positions"]:
+        args.steps = XL["n_positions"] - PROMPT - args.warmup - 4
     import torch
     config = dict(XL)
     layers = args.layers or XL["n_layer"]

@@ -262,12 +262,17 @@ class Engine:
         self._meta_recorded[self._turn] = True
         return slots, pos0
 
-    def _run(self, entries):
+    def _run(self, entries, device_ids=None):
         lengths = [len(e.tokens) for e in entries]
         N, E, M = sum(lengths), len(entries), sum(len(e.want) for e in entries)
         at = self._layout(N, E, M)
         decode_only = N == E
         slots, pos0 = self._upload(entries, lengths, at)
+        if device_ids is not None:
+            if device_ids.dtype != torch.int32 or device_ids.numel() != N or device_ids.device != self._meta_dev.device:
+                raise StepError("device_ids must be an int32 tensor on the engine's device with one id per token")
+            a, b = at["ids"]
+            self._meta_dev[a:b].copy_(device_ids.reshape(-1), non_blocking=True)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
         block = kernels.ATTENTION_PREFILL_TCGEN05_KEY_BLOCK
         aligned = not decode_only and all(p % block == 0 for p in pos0)
@@ -294,11 +299,18 @@ class Engine:
         ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
         return self.model.forward(ctx, self._caches)
 
+    accepts_device_ids = True          # step() can take the token ids of a decode step from a device tensor
+
     @torch.no_grad()
-    def step(self, entries, end=()):
+    def step(self, entries, end=(), device_ids=None):
         """Run one batch. Returns float32 logits [number of wanted places, vocab] in the order of
         the entries and of each entry's ``want`` (an empty [0, vocab] tensor if none are wanted).
         ``end``: requests that are finished after this step; what they hold is given back.
+        ``device_ids``: an int32 tensor on the device with one id per token of the step, in the order of
+        the entries, taken instead of the entries' own token values (which then only give the counts):
+        the sampler's output of the step before, so that this step can be launched before the host has
+        read those tokens. An id outside the vocabulary (the sampler's -1 for a row without a finite
+        maximum) sets error bit 1 on the device and its row computes nothing worth having.
         Raises StepError (bad batch) or PageCapacityError (no pages) with nothing changed.
         With CUDA graphs on, the logits of a step whose counts (tokens, entries, wanted places) were
         seen before live in a buffer that the next step of the same counts overwrites."""
@@ -313,7 +325,7 @@ class Engine:
             for r in fresh:
                 self.cache.release(r)
             raise
-        logits = self._run(entries)
+        logits = self._run(entries, device_ids)
         for e in entries:
             self.cache.advance(e.request, self.cache.length[e.request] + len(e.tokens))
         for r in end:

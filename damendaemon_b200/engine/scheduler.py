@@ -23,6 +23,14 @@ Decisions (the reference's, where it has them):
   out (damendaemon/scheduler.py:869-873).
 * A step that raises fails the requests in it and gives back their pages; the others go on
   (damendaemon/scheduler.py:812-818,881-895).
+* Running ahead. While only decoding requests are live, nothing waits and no request can end by
+  length in the step at hand, the next decode step is launched before this step's tokens are
+  read: the engine takes its token ids from the sampler's output on the device. The host's work
+  for a step then runs beside the device's, not between two steps. Only an end-of-sequence token
+  can end a request unforeseen; such a request took part in one step too many, whose row is
+  dropped, and everything it held goes back as always. Needs a sampler with ``launch`` and
+  ``read`` (the default has them) and page reservations; ``run_ahead=False`` switches it off.
+  The reference's scheduler reads every step's tokens before it plans the next.
 """
 from __future__ import annotations
 
@@ -72,9 +80,19 @@ class TokenEvent:
     finished: bool
 
 
+@dataclass
+class _InFlight:
+    """A step whose forward pass has been launched and whose tokens have not been handed out."""
+    entries: list                      # (request, tokens, want)
+    rows: list                         # the requests a token is sampled for, in the order of the logits
+    logits: object = None              # set while the sampling has not been launched yet
+    pending: object = None             # what sample_fn.launch returned
+    tokens: Optional[list] = None      # set when the sampler is a plain function: already read
+
+
 class Scheduler:
     def __init__(self, engine, *, token_budget=2048, chunk_size=0, max_live=None, reserve=True,
-                 length_policy="reject", sample_fn=None):
+                 length_policy="reject", sample_fn=None, run_ahead=True):
         if token_budget <= 0:
             raise ValueError("token_budget must be positive")
         if chunk_size < 0:
@@ -90,6 +108,11 @@ class Scheduler:
         if sample_fn is None:
             from ..sampling import sample_rows as sample_fn
         self.sample_fn = sample_fn
+        self._launch, self._read = getattr(sample_fn, "launch", None), getattr(sample_fn, "read", None)
+        self.run_ahead = bool(run_ahead and reserve and self._launch and self._read
+                              and getattr(engine, "accepts_device_ids", False))
+        self._in_flight = None
+        self.steps_ahead = 0     # steps whose forward pass was launched before the tokens of the step before were read
         self.waiting = deque()
         self.prefilling = []     # admitted, prompt not yet wholly in the cache; admission order
         self.decoding = []       # admitted, generating; admission order
@@ -168,32 +191,83 @@ class Scheduler:
         return [e for e in entries if any(e[0] is k[0] for k in kept)]
 
     # ------------------------------------------------------------------ one step
+    def _forward(self, entries, events, device_ids=None):
+        """Launch the step's forward pass and, unless the ids come from the device, its sampling.
+        A step that raises fails its requests; returns None then."""
+        try:
+            step_entries = [StepEntry(r.id, tokens, want) for r, tokens, want in entries]
+            if device_ids is None:
+                logits = self.engine.step(step_entries)
+            else:
+                logits = self.engine.step(step_entries, device_ids=device_ids)
+            flight = _InFlight(entries, [r for r, _, want in entries if want], logits=logits)
+            if device_ids is None:
+                self._sample(flight)
+            return flight
+        except Exception as error:      # the step failed: its requests fail, the others go on
+            for request, _, _ in entries:
+                if not request.finished:
+                    self._fail(request, f"{type(error).__name__}: {error}", events)
+            return None
+
+    def _sample(self, flight):
+        logits, flight.logits = flight.logits, None
+        if not flight.rows:
+            flight.tokens = []
+        elif self._launch and self._read:
+            flight.pending = self._launch(logits, [r.sampler for r in flight.rows])
+        else:
+            flight.tokens = self.sample_fn(logits, [r.sampler for r in flight.rows])
+
+    def _may_run_ahead(self, flight):
+        """Only decoding requests are live, all of them are in this step, nothing waits, and none of them
+        can end by length with the token this step samples."""
+        if not self.run_ahead or flight.pending is None or self.waiting or self.prefilling:
+            return False
+        if len(flight.rows) != len(self.decoding) or len(flight.entries) != len(flight.rows):
+            return False
+        for request in flight.rows:
+            if request not in self.decoding or len(request.output) + 1 >= request.max_tokens or \
+                    len(request.prompt) + len(request.output) + 1 >= self.engine.max_context:
+                return False
+        return True
+
     def step(self):
         """Admit, run one step of the engine, sample, finish. Returns the step's TokenEvents."""
         events = []
-        self._admit(events)
-        entries = self.plan()
-        if not entries:
-            if not self.reserve and self.live():
-                youngest = max(self.live(), key=lambda r: r.submitted_at)
-                self._fail(youngest, "cache_full", events)
-            return events
+        flight, self._in_flight = self._in_flight, None
+        if flight is None:
+            self._admit(events)
+            entries = self.plan()
+            if not entries:
+                if not self.reserve and self.live():
+                    youngest = max(self.live(), key=lambda r: r.submitted_at)
+                    self._fail(youngest, "cache_full", events)
+                return events
+            flight = self._forward(entries, events)
+            if flight is None:
+                return events
+        ahead = None
+        if self._may_run_ahead(flight):
+            # the token values are placeholders: the engine takes the ids from the sampler's output
+            ahead = self._forward([(r, [0], [0]) for r in flight.rows], events, device_ids=flight.pending.ids)
         try:
-            logits = self.engine.step([StepEntry(r.id, tokens, want) for r, tokens, want in entries])
-            rows = [r for r, _, want in entries if want]
-            tokens = self.sample_fn(logits, [r.sampler for r in rows]) if rows else []
-        except Exception as error:      # the step failed: its requests fail, the others go on
-            for request, _, _ in entries:
-                self._fail(request, f"{type(error).__name__}: {error}", events)
-            return events
+            tokens = flight.tokens if flight.tokens is not None else self._read(flight.pending)
+        except Exception as error:
+            for request, _, _ in flight.entries:
+                if not request.finished:
+                    self._fail(request, f"{type(error).__name__}: {error}", events)
+            return events               # a step launched ahead held the same requests: dropped with them
         self.steps += 1
-        self.step_log.append((sum(len(t) for r, t, _ in entries if r in self.prefilling),
-                              sum(1 for r, _, _ in entries if r in self.decoding)))
+        self.step_log.append((sum(len(t) for r, t, _ in flight.entries if r in self.prefilling),
+                              sum(1 for r, _, _ in flight.entries if r in self.decoding)))
         now = time.perf_counter()
-        for request, fed_tokens, _ in entries:
+        for request, fed_tokens, _ in flight.entries:
             if request in self.prefilling:
                 request.fed += len(fed_tokens)
-        for request, token in zip(rows, tokens):
+        for request, token in zip(flight.rows, tokens):
+            if request.finished:
+                continue                # it ended in the step before this one, which had been launched already
             if request in self.prefilling:
                 self.prefilling.remove(request)
                 self.decoding.append(request)
@@ -210,6 +284,15 @@ class Scheduler:
             if reason:
                 self._finish(request, reason)
             events.append(TokenEvent(request, token, reason is not None))
+        if ahead is not None and any(not r.finished for r in ahead.rows):
+            try:
+                self._sample(ahead)     # after this step's tokens were observed: penalties and draws are in order
+                self._in_flight = ahead
+                self.steps_ahead += 1
+            except Exception as error:
+                for request in ahead.rows:
+                    if not request.finished:
+                        self._fail(request, f"{type(error).__name__}: {error}", events)
         return events
 
     def _finish(self, request, reason):

@@ -10,11 +10,23 @@ class NonFiniteLogits(RuntimeError):
     pass
 
 
-def sample_rows(logits, samplers):
-    """logits: float32 [rows, vocab] on the device; samplers: one Sampler per row. Returns a list
-    of token ids. Greedy rows take the first maximum; sampled rows consume one draw of their
-    sampler's stream. A row without a finite maximum raises (the reference fails closed in the
-    same way, damendaemon/sampling.py:136-139)."""
+class PendingTokens:
+    """Sampled token ids that the host has not read yet: ``ids`` int32 [rows] on the device (what the
+    next step can take as its ``device_ids``), and their copy into pinned host memory, in flight."""
+    __slots__ = ("ids", "host", "event")
+
+    def __init__(self, ids):
+        self.ids = ids
+        self.host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
+        self.host.copy_(ids, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+
+def launch_sample_rows(logits, samplers):
+    """logits: float32 [rows, vocab] on the device; samplers: one Sampler per row. Launches the sampling
+    kernels and the copy of the ids to the host and returns a PendingTokens without waiting for either.
+    Greedy rows take the first maximum; sampled rows consume one draw of their sampler's stream."""
     rows = logits.shape[0]
     if rows != len(samplers) or logits.dim() != 2 or logits.shape[1] == 0:
         raise RuntimeError("invalid sampling logit batch")
@@ -46,7 +58,26 @@ def sample_rows(logits, samplers):
         if any(o.top_p < 1 for o in options):
             top_p = torch.tensor([float(o.top_p) for o in options], dtype=torch.float32, device=device)
         ids = kernels.sample(logits, temperature, uniform, top_k, top_p)
-    tokens = ids.tolist()
+    return PendingTokens(ids)
+
+
+def read_sampled(pending):
+    """Wait for the ids of launch_sample_rows (not for anything launched after it) and return them as
+    a list. A row without a finite maximum raises (the reference fails closed in the same way,
+    damendaemon/sampling.py:136-139)."""
+    pending.event.synchronize()
+    tokens = pending.host.tolist()
     if any(t < 0 for t in tokens):
         raise NonFiniteLogits("cannot sample non-finite model logits")
     return tokens
+
+
+def sample_rows(logits, samplers):
+    """Sample one token per row and return the ids as a list; see launch_sample_rows and read_sampled,
+    which are also reachable as ``sample_rows.launch`` and ``sample_rows.read`` (the scheduler uses
+    them to launch the next decode step before it reads this one's tokens)."""
+    return read_sampled(launch_sample_rows(logits, samplers))
+
+
+sample_rows.launch = launch_sample_rows
+sample_rows.read = read_sampled

@@ -15,6 +15,7 @@ class FakeEngine:
         self.max_context = max_context
         self.spec = SimpleNamespace(vocab_size=vocab, eos_token_ids=tuple(eos))
         self.calls = []
+        self.ahead_calls = []        # per call: were the token values taken from the sampler's output?
         self.fail_next = None
 
     def reserve(self, request, total, max_step):
@@ -34,7 +35,11 @@ class FakeEngine:
     def length(self, request):
         return self.cache.length.get(request, 0)
 
-    def step(self, entries):
+    accepts_device_ids = True
+
+    def step(self, entries, device_ids=None):
+        """device_ids: the token values of the step (one per entry) as the sampler left them, in place of
+        the entries' own: a list stands in for the device tensor."""
         if self.fail_next:
             error, self.fail_next = self.fail_next, None
             raise error
@@ -48,12 +53,14 @@ class FakeEngine:
                 self.cache.release(r)
             raise
         self.calls.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
+        self.ahead_calls.append(device_ids is not None)
         rows = []
-        for e in entries:
+        for i, e in enumerate(entries):
             self.cache.advance(e.request, self.cache.length[e.request] + len(e.tokens))
+            tokens = e.tokens if device_ids is None else [int(device_ids[i])]
             for w in e.want:
                 row = torch.zeros(self.spec.vocab_size)
-                row[(e.tokens[w] + 1) % self.spec.vocab_size] = 1.0
+                row[(tokens[w] + 1) % self.spec.vocab_size] = 1.0
                 rows.append(row)
         self.cache.check()
         return torch.stack(rows) if rows else torch.zeros(0, self.spec.vocab_size)
@@ -61,3 +68,17 @@ class FakeEngine:
 
 def greedy_cpu(logits, samplers):
     return logits.argmax(-1).tolist()
+
+
+class _Pending:
+    def __init__(self, ids):
+        self.ids = ids
+
+
+def greedy_cpu_in_two_parts(logits, samplers):
+    """The same choice, also offered as launch() and read(): the scheduler may then run ahead."""
+    return logits.argmax(-1).tolist()
+
+
+greedy_cpu_in_two_parts.launch = lambda logits, samplers: _Pending(logits.argmax(-1).tolist())
+greedy_cpu_in_two_parts.read = lambda pending: list(pending.ids)

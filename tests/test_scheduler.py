@@ -2,7 +2,7 @@
 import pytest
 
 from damendaemon_b200.engine.scheduler import Request, Scheduler
-from fake_engine import FakeEngine, greedy_cpu
+from fake_engine import FakeEngine, greedy_cpu, greedy_cpu_in_two_parts
 
 
 def make(engine=None, **kw):
@@ -134,3 +134,70 @@ def test_window_group_gives_pages_back_while_running():
     full, window = engine.cache.groups
     assert full.pool.high_water_pages == 8 and window.pool.high_water_pages <= 4
     assert r.finish_reason == "length" and engine.cache.used_tokens == 0
+
+
+# ---------------------------------------------------------------- running one decode step ahead
+
+def make_ahead(engine=None, **kw):
+    engine = engine or FakeEngine()
+    return engine, Scheduler(engine, sample_fn=greedy_cpu_in_two_parts, **kw)
+
+
+def test_running_ahead_gives_the_same_tokens_in_the_same_order():
+    prompts = [([1, 2, 3], 9), ([20], 5), ([40, 41], 12)]
+    runs = []
+    for ahead in (False, True):
+        engine, s = make_ahead(FakeEngine(kv_tokens=512), run_ahead=ahead)
+        rs = [s.submit(Request(list(p), max_tokens=n, ignore_eos=True)) for p, n in prompts]
+        events = drain(s)
+        runs.append(([r.output for r in rs], [(rs.index(e.request), e.token, e.finished) for e in events], s.steps))
+        assert (s.steps_ahead > 0) == ahead
+        assert any(engine.ahead_calls) == ahead
+        assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+    assert runs[0] == runs[1]
+
+
+def test_running_ahead_stops_before_a_request_can_end_by_length():
+    engine, s = make_ahead()
+    r = s.submit(Request([1, 2, 3], max_tokens=4, ignore_eos=True))
+    drain(s)
+    assert r.output == [4, 5, 6, 7] and r.finish_reason == "length"
+    # the prompt, the first decode step, then two steps launched before the tokens of the step before were read; the
+    # last of them samples the token with which the request ends, so nothing is launched after it
+    assert len(engine.calls) == 4 and engine.ahead_calls == [False, False, True, True]
+
+
+def test_end_of_sequence_while_running_ahead_drops_one_row():
+    engine, s = make_ahead(FakeEngine(kv_tokens=512))
+    a = s.submit(Request([5], max_tokens=20))                       # 6, 7, 8, 9 = end of sequence
+    b = s.submit(Request([30], max_tokens=8, ignore_eos=True))
+    events = drain(s)
+    assert a.output == [6, 7, 8, 9] and a.finish_reason == "stop"
+    assert b.output == list(range(31, 39)) and b.finish_reason == "length"
+    assert [e.token for e in events if e.request is a] == [6, 7, 8, 9]
+    # a took part in one step after its last token: that step had been launched already
+    assert sum(1 for call in engine.calls for (rid, n, want) in call if rid == a.id) == 5
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+
+
+def test_a_request_that_arrives_while_running_ahead_joins_after_the_step_in_flight():
+    engine, s = make_ahead(FakeEngine(kv_tokens=512))
+    a = s.submit(Request([1], max_tokens=30, ignore_eos=True))
+    for _ in range(4):
+        s.step()
+    assert s.steps_ahead >= 2
+    b = s.submit(Request([50, 51], max_tokens=3, ignore_eos=True))
+    drain(s)
+    assert a.output == list(range(2, 32)) and b.output == [52, 53, 54]
+    assert engine.cache.used_tokens == 0
+
+
+def test_a_failing_step_ahead_fails_its_requests_only_once():
+    engine, s = make_ahead(FakeEngine(kv_tokens=512))
+    a = s.submit(Request([1], max_tokens=30, ignore_eos=True))
+    s.step()
+    engine.fail_next = RuntimeError("device lost")
+    events = s.step() + drain(s)
+    assert a.finish_reason == "error" and "device lost" in a.error
+    assert sum(1 for e in events if e.request is a and e.token is None) == 1
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
