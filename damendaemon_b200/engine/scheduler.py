@@ -233,7 +233,8 @@ class Scheduler:
         return True
 
     def step(self):
-        """Admit, run one step of the engine, sample, finish. Returns the step's TokenEvents."""
+        """Admit, run one step of the engine, sample, finish. Returns the TokenEvents of the step whose
+        tokens it read: the one it launched, or the one a call before launched ahead."""
         events = []
         flight, self._in_flight = self._in_flight, None
         if flight is None:
