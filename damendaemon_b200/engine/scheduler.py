@@ -23,8 +23,8 @@ Decisions (the reference's, where it has them):
   out (damendaemon/scheduler.py:869-873).
 * A step that raises fails the requests in it and gives back their pages; the others go on
   (damendaemon/scheduler.py:812-818,881-895).
-* Running ahead. While only decoding requests are live, nothing waits and no request can end by
-  length in the step at hand, the next decode step is launched before this step's tokens are
+* Running ahead. While only decoding requests are live, nobody who waits can be admitted and no
+  request can end by length in the step at hand, the next decode step is launched before this step's tokens are
   read: the engine takes its token ids from the sampler's output on the device. The host's work
   for a step then runs beside the device's, not between two steps. Only an end-of-sequence token
   can end a request unforeseen; such a request took part in one step too many, whose row is
@@ -220,9 +220,9 @@ class Scheduler:
             flight.tokens = self.sample_fn(logits, [r.sampler for r in flight.rows])
 
     def _may_run_ahead(self, flight):
-        """Only decoding requests are live, all of them are in this step, nothing waits, and none of them
-        can end by length with the token this step samples."""
-        if not self.run_ahead or flight.pending is None or self.waiting or self.prefilling:
+        """Only decoding requests are live, all of them are in this step, nobody who waits can be admitted now
+        (the caller has tried), and none of them can end by length with the token this step samples."""
+        if not self.run_ahead or flight.pending is None or self.prefilling:
             return False
         if len(flight.rows) != len(self.decoding) or len(flight.entries) != len(flight.rows):
             return False
@@ -249,6 +249,8 @@ class Scheduler:
             if flight is None:
                 return events
         ahead = None
+        if self.waiting and self.run_ahead and flight.pending is not None:
+            self._admit(events)         # whoever can come in now makes the next step a mixed one: no running ahead then
         if self._may_run_ahead(flight):
             # the token values are placeholders: the engine takes the ids from the sampler's output
             ahead = self._forward([(r, [0], [0]) for r in flight.rows], events, device_ids=flight.pending.ids)

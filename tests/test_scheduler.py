@@ -201,3 +201,16 @@ def test_a_failing_step_ahead_fails_its_requests_only_once():
     assert a.finish_reason == "error" and "device lost" in a.error
     assert sum(1 for e in events if e.request is a and e.token is None) == 1
     assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+
+
+def test_running_ahead_goes_on_while_the_queue_is_blocked_and_admission_follows_the_end():
+    # pool of 4 pages (64 tokens): each request reserves 3 pages, so b waits until a has ended
+    engine, s = make_ahead(FakeEngine(kv_tokens=64, max_requests=4), token_budget=64)
+    a = s.submit(Request([1] * 30, max_tokens=10, ignore_eos=True))
+    b = s.submit(Request([2] * 30, max_tokens=10, ignore_eos=True))
+    drain(s)
+    assert a.output == list(range(2, 12)) and b.output == list(range(3, 13))
+    first_b = next(i for i, call in enumerate(engine.calls) if any(rid == b.id for rid, _, _ in call))
+    assert any(engine.ahead_calls[:first_b]), "a's decode steps did not run ahead while b waited"
+    assert all(rid == a.id for call in engine.calls[:first_b] for rid, _, _ in call)
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
