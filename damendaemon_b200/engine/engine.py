@@ -269,8 +269,6 @@ class Engine:
         decode_only = N == E
         slots, pos0 = self._upload(entries, lengths, at)
         if device_ids is not None:
-            if device_ids.dtype != torch.int32 or device_ids.numel() != N or device_ids.device != self._meta_dev.device:
-                raise StepError("device_ids must be an int32 tensor on the engine's device with one id per token")
             a, b = at["ids"]
             self._meta_dev[a:b].copy_(device_ids.reshape(-1), non_blocking=True)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
@@ -316,6 +314,10 @@ class Engine:
         seen before live in a buffer that the next step of the same counts overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
+        if device_ids is not None and (not torch.is_tensor(device_ids) or device_ids.dtype != torch.int32
+                                       or device_ids.numel() != sum(len(e.tokens) for e in entries)
+                                       or device_ids.device != self._meta_dev.device):
+            raise StepError("device_ids must be an int32 tensor on the engine's device with one id per token")
         fresh = [e.request for e in entries if e.request not in self.cache.slot_of]
         try:
             for r in fresh:

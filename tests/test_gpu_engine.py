@@ -148,6 +148,32 @@ def test_step_validation_changes_nothing(models):
     assert tuple(none.shape) == (0, 512)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_ids_from_the_device(models, dtype):
+    """A decode step whose token ids come from a device tensor (the sampler's output of the step before) gives the
+    logits of the same step fed from the host, bit for bit, eagerly and replayed from a graph; a tensor of the wrong
+    type or size is refused with nothing changed."""
+    from damendaemon_b200.engine import StepEntry, StepError
+    folder, config, requests, want = models["B", dtype]
+    prompts = {r: t[:9] for r, t in list(requests.items())[2:5]}
+    feed = [[(7 * s + 3 * i + 1) % config["vocab_size"] for i in range(len(prompts))] for s in range(5)]
+    host, device = engine_for(folder, dtype, 256, 8), engine_for(folder, dtype, 256, 8)
+    for engine in (host, device):
+        engine.step([StepEntry(r, t) for r, t in prompts.items()])
+    for ids in feed:
+        a = host.step([StepEntry(r, [ids[i]], [0]) for i, r in enumerate(prompts)]).clone()
+        on_device = torch.tensor(ids, dtype=torch.int32, device="cuda:0")
+        b = device.step([StepEntry(r, [0], [0]) for r in prompts], device_ids=on_device).clone()
+        assert torch.equal(a, b)
+    for bad in (torch.tensor(feed[0], dtype=torch.int64, device="cuda:0"), torch.zeros(2, dtype=torch.int32, device="cuda:0"),
+                torch.tensor(feed[0], dtype=torch.int32), feed[0]):
+        with pytest.raises(StepError):
+            device.step([StepEntry(r, [0], [0]) for r in prompts], device_ids=bad)
+        assert all(device.length(r) == host.length(r) for r in prompts)
+    device.cache.check()
+    assert device.raise_device_errors() is None
+
+
 def test_cache_that_does_not_fit_is_refused(models, monkeypatch):
     """The cache, a step's activations and the headroom are held against the free memory before the cache is
     allocated: a pool that cannot fit raises MemoryError and names what was asked for."""
