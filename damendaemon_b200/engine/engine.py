@@ -75,6 +75,8 @@ class Engine:
         self.weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
         self.page_size = page_size
         self.max_context = self.spec.max_positions
+        # where a scheduler should cut a prompt that it has to cut: at a key block of the bfloat16 prompt attention
+        self.portion_multiple = kernels.ATTENTION_PREFILL_TCGEN05_KEY_BLOCK if self.dtype == torch.bfloat16 else 1
         if kv_tokens is None:
             kv_tokens = max_requests * self.max_context
         kv_tokens = (kv_tokens + page_size - 1) // page_size * page_size

@@ -16,6 +16,8 @@ Decisions (the reference's, where it has them):
   budget with prompt portions of the admitted requests in admission order, each at most
   ``chunk_size`` tokens: one call of the step function, where the reference runs at most one
   chunk of one request and then a separate decode batch (damendaemon/scheduler.py:680-722,827-873).
+  A prompt that is cut is cut at a multiple of ``engine.portion_multiple`` tokens where the portion
+  is longer than that (the key block of the engine's prompt attention, 1 if it has none).
 * prompt + max_tokens must fit the context (damendaemon/prompts.py:4-9); with
   ``length_policy='clamp'`` max_tokens is cut to what fits instead.
 * A request ends on an end-of-sequence token (unless ignore_eos), at max_tokens ('length'),
@@ -107,6 +109,7 @@ class Scheduler:
         self.length_policy = length_policy
         if sample_fn is None:
             from ..sampling import sample_rows as sample_fn
+        self.portion_multiple = max(1, int(getattr(engine, "portion_multiple", 1)))
         self.sample_fn = sample_fn
         self._launch, self._read = getattr(sample_fn, "launch", None), getattr(sample_fn, "read", None)
         self.run_ahead = bool(run_ahead and reserve and self._launch and self._read
@@ -175,6 +178,10 @@ class Scheduler:
                 break
             n = min(len(request.prompt) - request.fed, self.chunk_size, budget)
             final = request.fed + n == len(request.prompt)
+            if not final and n > self.portion_multiple:
+                # a portion that is cut ends where the engine likes the next one to start (a key block of its prompt
+                # attention): the next portion then reads whole blocks and needs no separate cache write
+                n -= (request.fed + n) % self.portion_multiple
             entries.append((request, request.prompt[request.fed:request.fed + n], [n - 1] if final else []))
             budget -= n
         if not self.reserve:

@@ -214,3 +214,20 @@ def test_running_ahead_goes_on_while_the_queue_is_blocked_and_admission_follows_
     assert any(engine.ahead_calls[:first_b]), "a's decode steps did not run ahead while b waited"
     assert all(rid == a.id for call in engine.calls[:first_b] for rid, _, _ in call)
     assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+
+
+def test_a_prompt_is_cut_at_the_multiples_the_engine_asks_for():
+    engine = FakeEngine(kv_tokens=2048, max_context=1024)
+    engine.portion_multiple = 128
+    _, s = make(engine, token_budget=300)
+    a = s.submit(Request(list(range(1, 91)) * 7 + [5] * 70, max_tokens=2, ignore_eos=True))       # 700 tokens
+    drain(s)
+    assert [call[0][1] for call in engine.calls[:3]] == [256, 256, 188]
+    assert len(a.output) == 2
+    # a portion no longer than the multiple is left as the budget cuts it
+    engine = FakeEngine(kv_tokens=2048, max_context=1024)
+    engine.portion_multiple = 128
+    _, s = make(engine, token_budget=100)
+    s.submit(Request([3] * 250, max_tokens=1, ignore_eos=True))
+    drain(s)
+    assert [call[0][1] for call in engine.calls] == [100, 100, 50]
