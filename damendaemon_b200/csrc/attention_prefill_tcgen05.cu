@@ -1,28 +1,30 @@
 // Prompt-portion attention on the tcgen05 tensor cores, for bfloat16 caches and head size 64.
 //
-// A block owns 128 consecutive query tokens of one request and one head and walks the request's keys in blocks
-// of 128. Three roles:
-//   warp 0      TMA: the query tile once, then per key block either one box per cache page for the keys and one
+// A block owns a pair of tiles of 128 consecutive query tokens each (256 tokens of one request, one head) and walks
+// the request's keys in blocks of 128, which the two tiles share: the upper tile goes one block further than the
+// lower (with a window they may also start at different blocks). Three roles:
+//   warp 0      TMA: both query tiles once, then per key block either one box per cache page for the keys and one
 //               for the values (each lane issues one box), or, for a block that lies wholly in this step, one box
 //               of 128 rows each straight from the projection's output; several blocks ahead;
-//   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, accumulator in TMEM, two buffers so that the
-//               scores of block j+2 are computed while the softmax works on j and j+1), then O += P_j V_j
-//               (128 x 64, accumulated in TMEM over all blocks) with P read from tensor memory and V read as it
-//               lies in memory, as an MN-major operand;
-//   warps 2..9  softmax: two threads own one query row (its TMEM lane), one for each half of a block's 128 keys,
-//               so only the two halves' maxima are exchanged (shared memory, one barrier per block) and nothing is
-//               shuffled; a thread takes its 64 scores into registers with two TMEM loads in flight and writes P
-//               as bfloat16 pairs into tensor memory, over the first columns of the scores it came from. The
-//               exponentials, the row sum and the output are relative to a maximum that follows the true running
-//               maximum only when that has moved ahead by more than 8 (a factor of 256): only then does a thread
-//               rescale its half of the output row in TMEM, which is rare after the first blocks; the result is
-//               the same, since the sum is kept relative to the same maximum. float32 throughout.
+//   warp 1      one thread issues the MMAs: for each tile S_t = Q_t K^T (128 x 128, its own 128 TMEM columns) as
+//               soon as the tile's softmax warps hold the scores of its block before in registers, and
+//               O_t += P_t V (128 x 64, accumulated in TMEM over all blocks) for whichever tile has its P ready
+//               first, with P read from tensor memory (64 columns of its own per tile) and V read as it lies in
+//               memory, as an MN-major operand;
+//   warps 2..5 and 6..9  softmax of the lower and of the upper tile: a thread owns one query row (its TMEM lane),
+//               takes the row's 128 scores of a block into registers with four TMEM loads in flight, and writes
+//               P as bfloat16 pairs into tensor memory. Scaling and row sums use float32 pair instructions and
+//               the maximum a three-input instruction: the warps are bound by what they can issue as much as by
+//               the special-function unit. The exponentials, the row sum and the output are relative to a
+//               maximum that follows the true running maximum only when that has moved ahead by more than 8 (a
+//               factor of 256): only then does a thread rescale its output row in TMEM, which is rare after the
+//               first blocks; the result is the same, since the sum is kept relative to the same maximum.
 // Scores, softmax and the weighted sum of values are float32 (damendaemon/kernels.py:147-178 for the mask and
 // the stable softmax; damendaemon/qwen2.py:754-770 for the offset-aware causal rule). Keys outside the live
-// range (beyond the last query of the tile, before the window, pages that were given back) are never multiplied
+// range (beyond the last query of the pair, before the window, pages that were given back) are never multiplied
 // in: their scores are replaced, not scaled, and their value rows are zeroed in shared memory, so that stale
 // cache contents of any bit pattern cannot reach the result.
-// On request (store_new) the block also writes its tile's keys and values into the cache pages, by TMA from the
+// On request (store_new) the block also writes its tiles' keys and values into the cache pages, by TMA from the
 // shared memory they were loaded into, which saves the cache-write kernel and its pass over the projection's output.
 // Every wait is bounded; a wait that runs out sets the error flag and the block leaves through the common exit.
 #include "common.cuh"
