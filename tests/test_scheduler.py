@@ -231,3 +231,31 @@ def test_a_prompt_is_cut_at_the_multiples_the_engine_asks_for():
     s.submit(Request([3] * 250, max_tokens=1, ignore_eos=True))
     drain(s)
     assert [call[0][1] for call in engine.calls] == [100, 100, 50]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_running_ahead_under_random_arrivals_and_ends(seed):
+    """Random prompts, lengths, ends of sequence (the stand-in counts up and 9 ends a sequence) and arrivals between
+    steps, with a pool that makes requests wait: every request gets the same tokens and the same end with and
+    without running ahead, nothing is lost from the cache, and steps were in fact launched ahead."""
+    import random
+    outcomes = []
+    for ahead in (False, True):
+        rng = random.Random(seed)
+        engine, s = make_ahead(FakeEngine(kv_tokens=160, max_requests=3, max_context=64), token_budget=48, run_ahead=ahead)
+        requests, arrivals = [], sorted(rng.randrange(0, 40) for _ in range(10))
+        step = 0
+        while arrivals or not s.idle:
+            while arrivals and arrivals[0] <= step:
+                arrivals.pop(0)
+                prompt = [rng.randrange(0, 100) for _ in range(rng.randrange(1, 30))]
+                requests.append(s.submit(Request(prompt, max_tokens=rng.randrange(1, 25), ignore_eos=rng.random() < 0.3)))
+            s.step()
+            engine.cache.check()
+            step += 1
+            assert step < 2000
+        assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+        outcomes.append([(r.output, r.finish_reason) for r in requests])
+        if ahead:
+            assert s.steps_ahead > 0
+    assert outcomes[0] == outcomes[1]
