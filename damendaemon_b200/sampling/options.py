@@ -1,21 +1,92 @@
-"""Sampling options and per-request sampler state. Names, defaults and bounds are the
-reference's (damendaemon/sampling.py:17-58); the random stream is per request and never
-the global one (damendaemon/sampling.py:72-73)."""
+"""Sampling options and per-request sampler state.
+
+The option names, their defaults and their bounds are the reference's interface
+(damendaemon/sampling.py:17-58): temperature 0 = greedy, top_p in (0, 1], top_k 0 = off, a seed
+below 2**64, presence/frequency penalties in [-2, 2], a positive repetition penalty, at most 1,024
+biased tokens with biases in [-100, 100]. How they are checked is this project's: one table of
+(field, accepted type, range) walked once, and messages that quote the offending value.
+The random stream is per request and never the global one (damendaemon/sampling.py:72-73).
+"""
 from __future__ import annotations
 
-import math
 import random
 from collections import Counter
-from dataclasses import dataclass
+from dataclasses import dataclass, fields
+
+MAX_BIASED_TOKENS = 1024
+INF = float("inf")
 
 
-def _finite(value):
-    if type(value) not in (float, int):
-        return False
-    try:
-        return math.isfinite(value)
-    except OverflowError:
-        return False
+@dataclass(frozen=True)
+class _Range:
+    """An interval of real numbers with open or closed ends; ``whole`` asks for an int."""
+    low: float
+    high: float
+    low_open: bool = False
+    high_open: bool = False
+    whole: bool = False
+    optional: bool = False
+
+    def holds(self, value) -> bool:
+        if value is None:
+            return self.optional
+        # bool is an int to Python but not a number to a caller; huge ints compare exactly, no float() needed
+        if type(value) is not int and (self.whole or type(value) is not float):
+            return False
+        if value != value:           # NaN
+            return False
+        if type(value) is int and not self.whole and value.bit_length() > 1000:
+            return False             # an integer too large to become a float (JSON allows them)
+        above = value > self.low if self.low_open else value >= self.low
+        below = value < self.high if self.high_open else value <= self.high
+        return above and below
+
+    def __str__(self):
+        kind = "an integer" if self.whole else "a number"
+        left = "(" if self.low_open or self.low == -INF else "["
+        right = ")" if self.high_open or self.high == INF else "]"
+        text = f"{kind} in {left}{self.low:g}, {self.high:g}{right}"
+        return text + " or None" if self.optional else text
+
+
+RULES = {
+    "temperature": _Range(0, INF, high_open=True),
+    "top_p": _Range(0, 1, low_open=True),
+    "top_k": _Range(0, INF, high_open=True, whole=True),
+    "seed": _Range(0, 2 ** 64, high_open=True, whole=True, optional=True),
+    "presence_penalty": _Range(-2, 2),
+    "frequency_penalty": _Range(-2, 2),
+    "repetition_penalty": _Range(0, INF, low_open=True, high_open=True),
+}
+BIAS_VALUE = _Range(-100, 100)
+
+
+def _token_key(key):
+    """A bias table may come from JSON, whose keys are strings: '17' means token 17. Anything that is not
+    the canonical decimal spelling of a non-negative integer (' 17', '+17', '017', '١٧') is refused."""
+    if type(key) is int:
+        return key if key >= 0 else None
+    if isinstance(key, str) and key.isascii() and key.isdigit() and (key == "0" or key[0] != "0"):
+        return int(key)
+    return None
+
+
+def _checked_bias(table):
+    if not isinstance(table, dict):
+        raise ValueError(f"logit_bias: a dict of token id -> bias is expected, not {type(table).__name__}")
+    if len(table) > MAX_BIASED_TOKENS:
+        raise ValueError(f"logit_bias: {len(table)} tokens given, at most {MAX_BIASED_TOKENS} are taken")
+    out = {}
+    for key, value in table.items():
+        token = _token_key(key)
+        if token is None:
+            raise ValueError(f"logit_bias: {key!r} is not a token id")
+        if token in out:
+            raise ValueError(f"logit_bias: token {token} is given twice")
+        if not BIAS_VALUE.holds(value):
+            raise ValueError(f"logit_bias: the bias of token {token} is {value!r}; {BIAS_VALUE} is expected")
+        out[token] = value
+    return out
 
 
 @dataclass(frozen=True)
@@ -30,41 +101,21 @@ class Sampling:
     logit_bias: dict | None = None
 
     def __post_init__(self):
-        for name in ("temperature", "top_p"):
-            if not _finite(getattr(self, name)):
-                raise ValueError(f"{name} must be a finite number")
-        if self.temperature < 0 or not 0 < self.top_p <= 1:
-            raise ValueError("temperature must be nonnegative and top_p must be in (0, 1]")
-        if type(self.top_k) is not int or self.top_k < 0:
-            raise ValueError("top_k must be a nonnegative integer")
-        if self.seed is not None and (type(self.seed) is not int or not 0 <= self.seed < 2 ** 64):
-            raise ValueError("seed must be an integer in [0, 2**64)")
-        for name in ("presence_penalty", "frequency_penalty", "repetition_penalty"):
-            value = getattr(self, name)
-            if not _finite(value):
-                raise ValueError(f"{name} must be finite")
-            if (name == "repetition_penalty" and value <= 0) or (name != "repetition_penalty" and not -2 <= value <= 2):
-                raise ValueError("invalid token penalty")
-        bias = self.logit_bias
-        if bias is not None:
-            if not isinstance(bias, dict) or len(bias) > 1024:
-                raise ValueError("logit_bias must contain at most 1024 token entries")
-            normal = {}
-            for key, value in bias.items():
-                if isinstance(key, str) and key.isascii() and key.isdecimal() and str(int(key)) == key:
-                    key = int(key)
-                if type(key) is not int or key < 0 or key in normal or not _finite(value) or not -100 <= value <= 100:
-                    raise ValueError("invalid logit bias token or value")
-                normal[key] = value
-            object.__setattr__(self, "logit_bias", normal)
+        for f in fields(self):
+            rule = RULES.get(f.name)
+            value = getattr(self, f.name)
+            if rule is not None and not rule.holds(value):
+                raise ValueError(f"{f.name} is {value!r}; {rule} is expected")
+        if self.logit_bias is not None:
+            object.__setattr__(self, "logit_bias", _checked_bias(self.logit_bias))
 
     @property
     def greedy(self):
-        return not self.temperature
+        return self.temperature == 0
 
     @property
     def has_penalties(self):
-        return bool(self.presence_penalty or self.frequency_penalty or self.repetition_penalty != 1)
+        return self.presence_penalty != 0 or self.frequency_penalty != 0 or self.repetition_penalty != 1
 
     @property
     def has_adjustments(self):
@@ -76,18 +127,21 @@ class Sampler:
 
     def __init__(self, options: Sampling):
         self.options = options
-        self.random = random.Random(options.seed) if options.temperature else None
-        self.prompt_tokens = set()
+        self.random = None if options.greedy else random.Random(options.seed)
+        self.prompt_tokens = frozenset()
         self.counts = Counter()
 
     def prepare(self, prompt, vocab_size):
-        if any(token >= vocab_size for token in (self.options.logit_bias or {})):
-            raise ValueError("logit_bias token exceeds model vocabulary")
-        if self.options.repetition_penalty != 1:
-            self.prompt_tokens = set(prompt)
-        self.counts.clear()
+        """Called once when the request is taken in: the bias table is held against the model's vocabulary and
+        the prompt's tokens are remembered if the repetition penalty will want them."""
+        beyond = [t for t in (self.options.logit_bias or ()) if t >= vocab_size]
+        if beyond:
+            raise ValueError(f"logit_bias: token {min(beyond)} is outside the vocabulary of {vocab_size}")
+        self.prompt_tokens = frozenset(prompt) if self.options.repetition_penalty != 1 else frozenset()
+        self.counts = Counter()
 
     def observe(self, token):
+        """A token was generated for this request."""
         if self.options.has_penalties:
             self.counts[token] += 1
 
