@@ -43,6 +43,8 @@ def require_cuda(device):
     device = torch.device(device)
     if device.type != "cuda":
         raise kernels.KernelError(f"device {device} is not a CUDA device")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     return device
 
 
@@ -90,6 +92,7 @@ class Engine:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_graph = use_graph and self.model.graph_safe
         self._graphs, self._seen = {}, set()
+        self.graph_replays = 0                          # steps that ran as a replay of a captured graph
         self.max_graphs = 48                            # replayable step shapes kept; the least recently used goes first
         self.max_graph_tokens = 4096                    # larger steps run eagerly (a graph keeps its activations)
         kernels.error_flag(self.device)                 # allocated before any graph capture
@@ -171,6 +174,8 @@ class Engine:
             for w in e.want:
                 if type(w) is not int or not 0 <= w < n:
                     raise StepError(f"request {e.request!r}: wanted place {w!r} is not among its {n} tokens")
+            if len(set(e.want)) != len(e.want):
+                raise StepError(f"request {e.request!r}: a wanted place is named twice")
 
     def _meta_buffers(self, n_ints):
         if self._meta_dev is None or self._meta_dev.numel() < n_ints:
@@ -294,6 +299,7 @@ class Engine:
             if graph is not None:
                 self._graphs[key] = self._graphs.pop(key)        # most recently used last
                 graph[0].replay()
+                self.graph_replays += 1
                 return graph[1]             # valid until the next step of this shape
             self._seen.add(key)
         ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
@@ -318,7 +324,7 @@ class Engine:
         self._validate(entries)
         if device_ids is not None and (not torch.is_tensor(device_ids) or device_ids.dtype != torch.int32
                                        or device_ids.numel() != sum(len(e.tokens) for e in entries)
-                                       or device_ids.device != self._meta_dev.device):
+                                       or device_ids.device != self.device):
             raise StepError("device_ids must be an int32 tensor on the engine's device with one id per token")
         fresh = [e.request for e in entries if e.request not in self.cache.slot_of]
         try:

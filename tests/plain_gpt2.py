@@ -1,8 +1,9 @@
 """A plain, slow GPT-2: whole sequences, no cache, one function per part.
 
 It shares no code with the product path: it reads config.json and model.safetensors
-itself and computes with ordinary tensor arithmetic on the CPU (float64 by default,
-so that it is the more exact side of every comparison). Each function cites the
+itself and computes with ordinary tensor arithmetic (float64 by default, so that it is
+the more exact side of every comparison) on whatever device its weights lie: the CPU
+for the small models, a GPU for a model of the benchmark's full size. Each function cites the
 reference lines its formula comes from. The reference's own model code was run once
 on the CPU against this file (tests/golden/make_golden.py); the two options the
 reference rejects (exact-erf gelu and scaling by inverse layer index,
@@ -47,7 +48,7 @@ def read_folder(folder, dtype=torch.float64):
 
 def embed(ids, wte, wpe):
     """x[t] = wte[ids[t]] + wpe[t]  (damendaemon/gpt2.py:46; positions are arange, damendaemon/qwen2.py:866)."""
-    return wte[ids] + wpe[torch.arange(len(ids))]
+    return wte[ids] + wpe[torch.arange(len(ids), device=wte.device)]
 
 
 def layer_norm(x, gamma, beta, eps):
@@ -71,8 +72,8 @@ def causal_attention(q, k, v, scale, window=None):
     """
     T = q.shape[0]
     scores = torch.einsum("ihd,jhd->hij", q, k) * scale
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
     visible = j <= i
     if window is not None:
         visible = visible & (j > i - window)
@@ -118,7 +119,7 @@ def logits_of(config, w, ids, rounded=None, rows=None):
     moves the logits of a given model, which is what a bfloat16 tolerance has to allow for.
     """
     keep = (lambda t: t) if rounded is None else (lambda t: t.to(rounded).to(t.dtype))
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    ids = torch.as_tensor(ids, dtype=torch.long, device=w["wte.weight"].device)
     h, H = config["n_embd"], config["n_head"]
     T = len(ids)
     eps = config.get("layer_norm_epsilon", 1e-5)
@@ -139,7 +140,7 @@ def logits_of(config, w, ids, rounded=None, rows=None):
         g = keep(gelu_new(u) if activation == "gelu_new" else gelu_erf(u))
         x = x + conv1d(g, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
     if rows is not None:
-        x = x[torch.as_tensor(rows, dtype=torch.long)]       # the head only where it is asked for (damendaemon/gpt2.py:65)
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=x.device)]       # the head only where it is asked for (damendaemon/gpt2.py:65)
     x = keep(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps))
     return x @ w["wte.weight"].t()          # tied head, no bias (damendaemon/gpt2.py:18,66)
 

@@ -136,7 +136,8 @@ def test_step_validation_changes_nothing(models):
     engine = engine_for(folder, "float32", 64, 16)
     engine.step([StepEntry("a", [1, 2, 3])])
     for bad in ([StepEntry("a", [1]), StepEntry("a", [2])], [StepEntry("b", [])], [StepEntry("b", [512])],
-                [StepEntry("b", [-1])], [StepEntry("b", [1, 2], [2])], [StepEntry("b", [1] * 129)], []):
+                [StepEntry("b", [-1])], [StepEntry("b", [1, 2], [2])], [StepEntry("b", [1] * 129)], [],
+                [StepEntry("a", [1], [0, 0])], [StepEntry("b", [1, 2], [1, 1])]):
         with pytest.raises(StepError):
             engine.step(bad)
         assert engine.live_requests() == ["a"] and engine.length("a") == 3
@@ -165,6 +166,10 @@ def test_token_ids_from_the_device(models, dtype):
         on_device = torch.tensor(ids, dtype=torch.int32, device="cuda:0")
         b = device.step([StepEntry(r, [0], [0]) for r in prompts], device_ids=on_device).clone()
         assert torch.equal(a, b)
+    fresh = engine_for(folder, dtype, 256, 8)           # a first step with a bad tensor: refused in the same way
+    with pytest.raises(StepError):
+        fresh.step([StepEntry("x", [1], [0])], device_ids=torch.tensor([1], dtype=torch.int32))
+    assert not fresh.live_requests()
     for bad in (torch.tensor(feed[0], dtype=torch.int64, device="cuda:0"), torch.zeros(2, dtype=torch.int32, device="cuda:0"),
                 torch.tensor(feed[0], dtype=torch.int32), feed[0]):
         with pytest.raises(StepError):

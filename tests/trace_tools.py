@@ -34,18 +34,23 @@ def run_trace(model_dir, dtype, steps, out_dir, max_tokens, page_size=16, timeou
 class TraceBuilder:
     """Collects steps and remembers which (request, position) each wanted row is."""
 
-    def __init__(self):
+    def __init__(self, wanted=None):
+        """wanted: {request: positions whose logits are asked for}; None = every position."""
         self.steps = []
         self.where = {}       # step -> [(request, position)]
         self.fed = {}         # request -> tokens fed so far
+        self.wanted = wanted
 
     def step(self, parts, end=()):
-        """parts: [(request, tokens, want_all: bool)]"""
+        """parts: [(request, tokens, want: bool)]; where ``wanted`` was given, a part that wants logits
+        asks for those of its positions that are in its request's set."""
         number = len(self.steps)
         entries, where = [], []
         for request, tokens, want_all in parts:
             start = self.fed.get(request, 0)
             want = list(range(len(tokens))) if want_all else []
+            if self.wanted is not None:
+                want = [i for i in want if start + i in self.wanted[request]]
             entries.append({"id": request, "tokens": list(tokens), "want": want})
             where += [(request, start + w) for w in want]
             self.fed[request] = start + len(tokens)
@@ -68,17 +73,17 @@ def round64(n):
     return (n + 63) // 64 * 64
 
 
-def whole_steps(requests):
+def whole_steps(requests, wanted=None):
     """Each request alone and whole, every position wanted."""
-    b = TraceBuilder()
+    b = TraceBuilder(wanted)
     for r, tokens in requests.items():
         b.step([(r, tokens, True)], end=[r])
     return b
 
 
-def tail_steps(requests, tail=32):
+def tail_steps(requests, tail=32, wanted=None):
     """Most of a request in one step, its last `tail` tokens one by one."""
-    b = TraceBuilder()
+    b = TraceBuilder(wanted)
     for r, tokens in requests.items():
         head = max(1, len(tokens) - tail)
         b.step([(r, tokens[:head], True)])
@@ -89,9 +94,9 @@ def tail_steps(requests, tail=32):
     return b
 
 
-def portion_steps(requests, sizes=(7, 2, 16, 3, 2, 33, 5, 2, 64, 1)):
+def portion_steps(requests, sizes=(7, 2, 16, 3, 2, 33, 5, 2, 64, 1), wanted=None):
     """Portions of changing size, down to two tokens (and one)."""
-    b = TraceBuilder()
+    b = TraceBuilder(wanted)
     for r, tokens in requests.items():
         at, i = 0, 0
         while at < len(tokens):
@@ -101,13 +106,13 @@ def portion_steps(requests, sizes=(7, 2, 16, 3, 2, 33, 5, 2, 64, 1)):
     return b
 
 
-def mixed_steps(requests, seed=0, max_live=4, prompt_share=0.6):
+def mixed_steps(requests, seed=0, max_live=4, prompt_share=0.6, wanted=None, portions=(2, 3, 5, 8, 13, 17, 32)):
     """Up to max_live requests at a time: portions of some beside decoded tokens of others,
     requests now and then left out of a step. Returns (builder, most tokens held at once, each
     request's count rounded up to 64)."""
     import random
     rng = random.Random(seed)
-    b = TraceBuilder()
+    b = TraceBuilder(wanted)
     waiting = list(requests)
     live, at = [], {}
     peak = 0
@@ -123,7 +128,7 @@ def mixed_steps(requests, seed=0, max_live=4, prompt_share=0.6):
                 continue
             left = len(tokens) - at[r]
             if at[r] < int(prompt_share * len(tokens)):
-                n = min(left, rng.choice((2, 3, 5, 8, 13, 17, 32)))
+                n = min(left, rng.choice(portions))
             else:
                 n = 1
             parts.append((r, tokens[at[r]:at[r] + n], True))
