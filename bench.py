@@ -173,7 +173,7 @@ def decode_end_to_end(runtime, batch, warmup, steps, vocab):
     h2d = runtime.engine.last_h2d_bytes
     for r in scheduler.live():
         runtime.engine.finish(r.id)
-    return produced / wall, h2d, batch * 4
+    return produced / wall, h2d, (batch + 1) * 4     # the sampled ids and the kernels' error word
 
 
 def prefill_timed(engine, vocab, repeats=5):

@@ -33,6 +33,14 @@ Decisions (the reference's, where it has them):
   dropped, and everything it held goes back as always. Needs a sampler with ``launch`` and
   ``read`` (the default has them) and page reservations; ``run_ahead=False`` switches it off.
   The reference's scheduler reads every step's tokens before it plans the next.
+* A request can be withdrawn (``cancel``) while it waits, between two portions of its prompt, or while it
+  decodes, also with a step launched ahead that still holds it (that step's row for it is dropped, as after an
+  end-of-sequence token). What it holds, pages and promise, goes back before its last event is handed out; its
+  finish reason is 'cancelled' (damendaemon/scheduler.py:856-862 frees a cancelled request's slot in the same turn).
+* With ``queue_timeout`` (seconds) a request that has waited that long for its pages fails with
+  'KV admission timeout' (damendaemon/scheduler.py:758-761); the ones behind it move up.
+* ``max_context`` caps prompt + generated tokens below the model's positions (a runtime whose page pool was sized
+  for a shorter context).
 """
 from __future__ import annotations
 
@@ -65,6 +73,7 @@ class Request:
     submitted_at: float = 0.0
     first_token_at: Optional[float] = None
     finished_at: Optional[float] = None
+    cancel_requested: bool = False
 
     def __post_init__(self):
         if self.id is None:
@@ -94,14 +103,22 @@ class _InFlight:
 
 class Scheduler:
     def __init__(self, engine, *, token_budget=2048, chunk_size=0, max_live=None, reserve=True,
-                 length_policy="reject", sample_fn=None, run_ahead=True):
+                 length_policy="reject", sample_fn=None, run_ahead=True, queue_timeout=None, max_context=None,
+                 clock=time.monotonic):
         if token_budget <= 0:
             raise ValueError("token_budget must be positive")
         if chunk_size < 0:
             raise ValueError("chunk_size must be 0 (no limit below the budget) or positive")
         if length_policy not in ("reject", "clamp"):
             raise ValueError("length_policy must be 'reject' or 'clamp'")
+        if queue_timeout is not None and not queue_timeout > 0:
+            raise ValueError("queue_timeout must be positive seconds, or None for no limit")
+        if max_context is not None and not 0 < max_context <= engine.max_context:
+            raise ValueError(f"max_context must be between 1 and the model's {engine.max_context} positions")
         self.engine = engine
+        self.max_context = max_context or engine.max_context
+        self.queue_timeout = queue_timeout
+        self.clock = clock
         self.token_budget = token_budget
         self.chunk_size = chunk_size or token_budget
         self.max_live = min(max_live or engine.cache.max_requests, engine.cache.max_requests)
@@ -125,7 +142,7 @@ class Scheduler:
 
     # ------------------------------------------------------------------ intake
     def submit(self, request: Request) -> Request:
-        context, vocab = self.engine.max_context, self.engine.spec.vocab_size
+        context, vocab = self.max_context, self.engine.spec.vocab_size
         if not isinstance(request.prompt, list) or not request.prompt or \
                 any(type(t) is not int or not 0 <= t < vocab for t in request.prompt):
             raise ValueError("prompt must be a nonempty list of token ids inside the vocabulary")
@@ -138,8 +155,33 @@ class Scheduler:
         request.sampler = Sampler(request.sampling)
         request.sampler.prepare(request.prompt, vocab)
         request.submitted_at = time.perf_counter()
+        request.waiting_since = self.clock()
         self.waiting.append(request)
         return request
+
+    def cancel(self, request) -> bool:
+        """Withdraw a request (the object ``submit`` returned, or its id). It takes effect at the start of the next
+        ``step()``: whatever the request holds goes back, and that step's events end with its terminal event
+        (token None, finish reason 'cancelled'). Returns False if the request is unknown or has ended already.
+        Setting the flag is all this does, so another thread may call it while ``step()`` runs."""
+        for known in itertools.chain(self.waiting, self.prefilling, self.decoding):
+            if known is request or known.id == request:
+                known.cancel_requested = True
+                return True
+        return False
+
+    def _withdraw(self, events):
+        """Apply cancellations and the queue timeout; runs before anything else in a step."""
+        for request in [r for r in self.live() if r.cancel_requested]:
+            self._end(request, "cancelled", None, events)
+        now = self.clock()
+        for request in list(self.waiting):
+            if request.cancel_requested:
+                self.waiting.remove(request)
+                self._end(request, "cancelled", None, events, release=False)
+            elif self.queue_timeout is not None and now - request.waiting_since > self.queue_timeout:
+                self.waiting.remove(request)
+                self._end(request, "error", "KV admission timeout", events, release=False)
 
     @property
     def idle(self):
@@ -235,7 +277,7 @@ class Scheduler:
             return False
         for request in flight.rows:
             if request not in self.decoding or len(request.output) + 1 >= request.max_tokens or \
-                    len(request.prompt) + len(request.output) + 1 >= self.engine.max_context:
+                    len(request.prompt) + len(request.output) + 1 >= self.max_context:
                 return False
         return True
 
@@ -243,7 +285,10 @@ class Scheduler:
         """Admit, run one step of the engine, sample, finish. Returns the TokenEvents of the step whose
         tokens it read: the one it launched, or the one a call before launched ahead."""
         events = []
+        self._withdraw(events)
         flight, self._in_flight = self._in_flight, None
+        if flight is not None and all(r.finished for r, _, _ in flight.entries):
+            flight = None               # everybody the step launched ahead was for has been withdrawn
         if flight is None:
             self._admit(events)
             entries = self.plan()
@@ -289,7 +334,7 @@ class Scheduler:
                 reason = "stop"
             elif len(request.output) >= request.max_tokens:
                 reason = "length"
-            elif len(request.prompt) + len(request.output) >= self.engine.max_context:
+            elif len(request.prompt) + len(request.output) >= self.max_context:
                 reason = "length"
             if reason:
                 self._finish(request, reason)
@@ -315,9 +360,13 @@ class Scheduler:
         self.done.append(request)
 
     def _fail(self, request, message, events, release=True):
+        self._end(request, "error", message, events, release)
+
+    def _end(self, request, reason, message, events, release=True):
+        """End a request without a token: what it holds goes back first, then its terminal event is queued."""
         if release:
             self.engine.finish(request.id)
-        request.finish_reason, request.error = "error", message
+        request.finish_reason, request.error = reason, message
         request.finished_at = time.perf_counter()
         for group in (self.prefilling, self.decoding):
             if request in group:

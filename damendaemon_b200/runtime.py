@@ -17,12 +17,13 @@ from .sampling import Sampling
 class Runtime:
     def __init__(self, model, context=None, *, dtype="bfloat16", kv_cache_tokens=None, max_batch=16, page_size=16,
                  device="cuda:0", use_graph=True, prefill_chunk_size=0, token_budget=4096, config=None, tensors=None,
-                 run_ahead=True):
+                 run_ahead=True, queue_timeout=None):
         """model: a folder with config.json and model.safetensors (or None with config= and tensors=).
         context: most tokens a request may hold (default: the model's positions).
         kv_cache_tokens: size of the shared page pool in tokens (default: max_batch * context).
         prefill_chunk_size: largest prompt portion per step, 0 = up to the token budget.
-        run_ahead: launch the next decode step before this step's tokens are read (see the scheduler)."""
+        run_ahead: launch the next decode step before this step's tokens are read (see the scheduler).
+        queue_timeout: seconds a request may wait for cache pages before it fails (None: no limit)."""
         self.engine = Engine(model, config=config, tensors=tensors, dtype=dtype, page_size=page_size,
                              max_requests=max_batch, device=device,
                              kv_tokens=kv_cache_tokens or max_batch * min(context or 10 ** 9, _positions(model, config)),
@@ -31,6 +32,7 @@ class Runtime:
         self.prefill_chunk_size = prefill_chunk_size
         self.token_budget = token_budget
         self.run_ahead = run_ahead
+        self.queue_timeout = queue_timeout
         self.tokenizer = _load_tokenizer(model)
 
     # ------------------------------------------------------------------ helpers
@@ -45,7 +47,8 @@ class Runtime:
 
     def _scheduler(self, length_policy="reject"):
         return Scheduler(self.engine, token_budget=self.token_budget, chunk_size=self.prefill_chunk_size,
-                         length_policy=length_policy, run_ahead=self.run_ahead)
+                         length_policy=length_policy, run_ahead=self.run_ahead, max_context=self.context,
+                         queue_timeout=self.queue_timeout)
 
     def _text(self, tokens):
         return self.tokenizer.decode(tokens) if self.tokenizer is not None else ""

@@ -1,4 +1,4 @@
 from .options import Sampler, Sampling
-from .select import NonFiniteLogits, sample_rows
+from .select import DeviceStepError, NonFiniteLogits, sample_rows
 
-__all__ = ["Sampler", "Sampling", "NonFiniteLogits", "sample_rows"]
+__all__ = ["Sampler", "Sampling", "DeviceStepError", "NonFiniteLogits", "sample_rows"]

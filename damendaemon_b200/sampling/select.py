@@ -10,15 +10,24 @@ class NonFiniteLogits(RuntimeError):
     pass
 
 
+class DeviceStepError(RuntimeError):
+    """A kernel of the step whose tokens are being read set an error bit; the tokens are not to be trusted."""
+
+
 class PendingTokens:
     """Sampled token ids that the host has not read yet: ``ids`` int32 [rows] on the device (what the
-    next step can take as its ``device_ids``), and their copy into pinned host memory, in flight."""
-    __slots__ = ("ids", "host", "event")
+    next step can take as its ``device_ids``), and their copy into pinned host memory, in flight.
+    The kernels' error word of the device travels in the same pinned buffer, behind the ids, under the
+    same event: reading the tokens also tells whether a kernel up to this step reported a missing page,
+    a bad token or a wait that ran out, without another synchronisation."""
+    __slots__ = ("ids", "host", "event", "rows")
 
     def __init__(self, ids):
         self.ids = ids
-        self.host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
-        self.host.copy_(ids, non_blocking=True)
+        self.rows = ids.numel()
+        self.host = torch.empty(self.rows + 1, dtype=torch.int32, pin_memory=True)
+        self.host[:self.rows].copy_(ids.reshape(-1), non_blocking=True)
+        self.host[self.rows:].copy_(kernels.error_flag(ids.device), non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record()
 
@@ -64,9 +73,15 @@ def launch_sample_rows(logits, samplers):
 def read_sampled(pending):
     """Wait for the ids of launch_sample_rows (not for anything launched after it) and return them as
     a list. A row without a finite maximum raises (the reference fails closed in the same way,
-    damendaemon/sampling.py:136-139)."""
+    damendaemon/sampling.py:136-139); so does an error bit that a kernel of this step, or of one before it
+    that nobody has read, left in the device's error word (the word is cleared)."""
     pending.event.synchronize()
-    tokens = pending.host.tolist()
+    *tokens, bits = pending.host.tolist()
+    if bits:
+        # in stream order this clears the word after every step launched so far, the one launched ahead included
+        kernels.error_flag(pending.ids.device).zero_()
+        raise DeviceStepError(f"a kernel reported error bits {bits:#x} (1 bad token/position, 2 bad page on write, "
+                              "4 bad page on read, 8 wait timed out)")
     if any(t < 0 for t in tokens):
         raise NonFiniteLogits("cannot sample non-finite model logits")
     return tokens

@@ -75,11 +75,11 @@ def test_replayed_prompt_and_mixed_steps(model_c, dtype):
         for r in tokens:
             engine.finish(r)
         engine.cache.check()
-    # Four shapes come back and are captured at their second appearance, replayed from the third on: the first portions
+    # Four shapes come back; each is captured at its second appearance and runs as a replay from then on: the first portions
     # (5 times), the second portions off a key-block boundary (4 times; the trial whose second portions start at 128 has
     # the same counts but starts on boundaries, another shape, seen once), the mixed step (5), the decode step (15).
     assert len(engine._graphs) == 4
-    assert engine.graph_replays == 3 + 2 + 3 + 13
+    assert engine.graph_replays == 4 + 3 + 4 + 14
     assert engine.raise_device_errors() is None and checked == len(trials) * 22
 
 

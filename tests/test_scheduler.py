@@ -259,3 +259,165 @@ def test_running_ahead_under_random_arrivals_and_ends(seed):
         if ahead:
             assert s.steps_ahead > 0
     assert outcomes[0] == outcomes[1]
+
+
+# ---------------------------------------------------------------- withdrawing a request; waiting too long
+
+class Clock:
+    def __init__(self):
+        self.now = 0.0
+
+    def __call__(self):
+        return self.now
+
+
+def ended(events, request):
+    return [e for e in events if e.request is request and e.finished and e.token is None]
+
+
+def test_cancel_while_waiting_lets_the_next_one_move_up():
+    # pool of 4 pages: a holds 3, b (3 pages) waits at the head, c (1 page) behind it
+    engine, s = make(FakeEngine(kv_tokens=64, max_requests=4), token_budget=64)
+    a = s.submit(Request([1] * 30, max_tokens=10, ignore_eos=True))
+    b = s.submit(Request([2] * 30, max_tokens=10, ignore_eos=True))
+    c = s.submit(Request([3], max_tokens=2, ignore_eos=True))
+    s.step()
+    assert list(s.waiting) == [b, c]
+    assert s.cancel(b) and not s.cancel("nobody")
+    events = s.step()
+    assert b.finish_reason == "cancelled" and b.error is None and len(ended(events, b)) == 1 and not b.output
+    assert c in s.live(), "c fits beside a once b is gone"
+    assert not s.cancel(b), "it has ended already"
+    drain(s)
+    assert a.finish_reason == c.finish_reason == "length" and c.output == [4, 5]
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+    engine.cache.check()
+
+
+def test_cancel_between_portions_gives_pages_and_promise_back():
+    engine, s = make(FakeEngine(kv_tokens=128, max_context=128), token_budget=16)
+    a = s.submit(Request([1] * 50, max_tokens=10, ignore_eos=True))
+    s.step(); s.step()
+    assert a.fed == 32 and engine.cache.used_tokens == 32
+    pool = engine.cache.groups[0].pool
+    assert pool.unpromised_pages < pool.n_pages - 2
+    s.cancel(a.id)
+    events = s.step()
+    assert a.finish_reason == "cancelled" and len(ended(events, a)) == 1
+    assert engine.cache.used_tokens == 0 and pool.unpromised_pages == pool.n_pages and not engine.cache.slot_of
+    assert s.idle and len(engine.calls) == 2, "no step ran for it after the cancellation"
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_cancel_while_decoding(ahead):
+    """With a step launched ahead that still holds the request, that step's row for it is dropped; the other
+    request's tokens are what they would have been."""
+    engine, s = make_ahead(FakeEngine(kv_tokens=512), run_ahead=ahead)
+    a = s.submit(Request([1], max_tokens=40, ignore_eos=True))
+    b = s.submit(Request([50], max_tokens=12, ignore_eos=True))
+    for _ in range(5):
+        s.step()
+    assert (s._in_flight is not None) == ahead
+    had = len(a.output)
+    s.cancel(a)
+    events = s.step()
+    assert a.finish_reason == "cancelled" and len(a.output) == had and len(ended(events, a)) == 1
+    assert a.id not in engine.cache.slot_of
+    rest = events + drain(s)
+    assert b.output == list(range(51, 63)) and b.finish_reason == "length"
+    assert not [e for e in rest if e.request is a and e.token is not None]
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+    engine.cache.check()
+
+
+def test_cancel_of_the_only_request_with_a_step_in_flight():
+    engine, s = make_ahead(FakeEngine(kv_tokens=512))
+    a = s.submit(Request([1], max_tokens=40, ignore_eos=True))
+    for _ in range(4):
+        s.step()
+    assert s._in_flight is not None
+    s.cancel(a)
+    events = s.step()
+    assert [e.token for e in events] == [None] and a.finish_reason == "cancelled"
+    assert s.idle and s._in_flight is None and engine.cache.used_tokens == 0
+    b = s.submit(Request([7], max_tokens=2, ignore_eos=True))        # the scheduler goes on as before
+    drain(s)
+    assert b.output == [8, 9]
+
+
+def test_queue_timeout_fails_a_request_that_waits_too_long():
+    clock = Clock()
+    engine, s = make(FakeEngine(kv_tokens=64, max_requests=4), token_budget=64, queue_timeout=5.0, clock=clock)
+    a = s.submit(Request([1] * 30, max_tokens=30, ignore_eos=True))
+    b = s.submit(Request([2] * 30, max_tokens=10, ignore_eos=True))      # cannot be promised pages beside a
+    clock.now = 1.0
+    c = s.submit(Request([3] * 30, max_tokens=10, ignore_eos=True))
+    s.step()
+    assert list(s.waiting) == [b, c]
+    clock.now = 5.5
+    events = s.step()
+    assert b.finish_reason == "error" and b.error == "KV admission timeout" and len(ended(events, b)) == 1
+    assert list(s.waiting) == [c], "c came later and has waited 4.5 s"
+    clock.now = 6.5
+    s.step()
+    assert c.finish_reason == "error" and c.error == "KV admission timeout"
+    drain(s)
+    assert a.finish_reason == "length" and len(a.output) == 30
+    assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+    engine.cache.check()
+    # an admitted request is never timed out, however long it runs
+    d = s.submit(Request([4] * 10, max_tokens=20, ignore_eos=True))
+    s.step()
+    clock.now = 100.0
+    drain(s)
+    assert d.finish_reason == "length"
+    with pytest.raises(ValueError):
+        Scheduler(FakeEngine(), queue_timeout=0)
+
+
+def test_max_context_below_the_models_positions():
+    engine, s = make(FakeEngine(kv_tokens=256, max_context=128), max_context=40)
+    with pytest.raises(ValueError, match="exceeds"):
+        s.submit(Request([1] * 30, max_tokens=11))
+    r = s.submit(Request([1] * 30, max_tokens=10, ignore_eos=True))
+    drain(s)
+    assert len(r.output) == 10
+    engine, s = make(FakeEngine(kv_tokens=256, max_context=128), max_context=40, length_policy="clamp")
+    r = s.submit(Request([1] * 30, max_tokens=100, ignore_eos=True))
+    drain(s)
+    assert len(r.output) == 10 and r.finish_reason == "length"
+    with pytest.raises(ValueError):
+        Scheduler(FakeEngine(max_context=128), max_context=129)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_cancellations_lose_nothing(seed):
+    """Random arrivals, ends and cancellations at any stage, with and without running ahead: every request ends exactly
+    once, a cancelled one gets no token after its cancellation took effect, and nothing is lost from the cache."""
+    import random
+    for ahead in (False, True):
+        rng = random.Random(seed)
+        engine, s = make_ahead(FakeEngine(kv_tokens=160, max_requests=3, max_context=64), token_budget=24, run_ahead=ahead)
+        requests, terminal, step = [], {}, 0
+        arrivals = sorted(rng.randrange(0, 40) for _ in range(12))
+        while arrivals or not s.idle:
+            while arrivals and arrivals[0] <= step:
+                arrivals.pop(0)
+                prompt = [rng.randrange(0, 100) for _ in range(rng.randrange(1, 40))]
+                requests.append(s.submit(Request(prompt, max_tokens=rng.randrange(1, 20), ignore_eos=rng.random() < 0.5)))
+            if requests and rng.random() < 0.2:
+                s.cancel(rng.choice(requests))
+            for e in s.step():
+                if e.finished:
+                    assert e.request.id not in terminal
+                    terminal[e.request.id] = e
+                else:
+                    assert e.request.id not in terminal, "a token after the terminal event"
+            engine.cache.check()
+            step += 1
+            assert step < 2000
+        assert set(terminal) == {r.id for r in requests}
+        assert any(r.finish_reason == "cancelled" for r in requests)
+        assert engine.cache.used_tokens == 0 and not engine.cache.slot_of
+        assert engine.cache.groups[0].pool.unpromised_pages == engine.cache.groups[0].pool.n_pages
