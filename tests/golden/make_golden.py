@@ -14,6 +14,13 @@ Configuration A runs as it is. Configuration B uses exact-erf gelu and scaling b
 inverse layer index, both of which the reference refuses (damendaemon/config.py:301-303);
 "B-prime" keeps B's sizes with gelu_new and no layer scaling so that head size 48,
 explicit n_inner, eps 1e-6 and 3 layers are still anchored.
+
+Scaling by inverse layer index is anchored all the same, through an identity: dividing
+the scores of layer i by (i + 1) is dividing its queries by (i + 1), and the queries
+are c_attn's first third. "Bscaled" therefore gives the reference B-prime's weights
+with the query columns and query bias of layer i divided by (i + 1) and the option
+off, which it accepts; the test holds the plain implementation, run on the unchanged
+B-prime weights WITH the option on, to those logits.
 """
 import json
 import sys
@@ -31,11 +38,34 @@ sys.path.insert(0, str(HERE.parent))
 from conftest import TINY_A, TINY_B  # noqa: E402
 from damendaemon_b200.weights import write_random_model  # noqa: E402
 
+B_PRIME = {**TINY_B, "activation_function": "gelu_new", "scale_attn_by_inverse_layer_idx": False}
+# name: (the configuration the plain implementation runs, seed, groups of prompt lengths)
 CASES = {
     "A": (dict(TINY_A), 0, [[5, 17], [33]]),
-    "Bprime": ({**TINY_B, "activation_function": "gelu_new", "scale_attn_by_inverse_layer_idx": False}, 1, [[9, 64], [200]]),
+    "Bprime": (dict(B_PRIME), 1, [[9, 64], [200]]),
+    "Bscaled": ({**B_PRIME, "scale_attn_by_inverse_layer_idx": True}, 1, [[9, 64], [200]]),
 }
 DECODE_STEPS = 4
+
+
+def folder_for_the_reference(folder, config, seed):
+    """The model folder the reference is given for a case. A configuration with scaling by inverse layer index
+    becomes one without it whose queries are divided by (layer index + 1) in the weights."""
+    from damendaemon_b200.registry import architecture_of
+    from damendaemon_b200.weights import write_safetensors
+    if not config.get("scale_attn_by_inverse_layer_idx"):
+        return write_random_model(folder, {**config, "eos_token_id": 0}, seed, "float32", name_prefix="transformer.")
+    plain_config = {**config, "scale_attn_by_inverse_layer_idx": False, "eos_token_id": 0}
+    arch = architecture_of(config)
+    tensors = arch.random_tensors(arch.parse_config(config), seed, torch.float32)
+    h = config["n_embd"]
+    for i in range(config["n_layer"]):
+        tensors[f"h.{i}.attn.c_attn.weight"][:, :h] /= (i + 1)        # Conv1D [in, out]: the first third of the outputs
+        tensors[f"h.{i}.attn.c_attn.bias"][:h] /= (i + 1)
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(arch.parse_config(plain_config).to_dict()))
+    write_safetensors(folder / "model.safetensors", {"transformer." + k: v for k, v in tensors.items()})
+    return folder
 
 
 def prompts_for(config, lengths, seed):
@@ -50,7 +80,7 @@ def main(reference_root):
     out = {}
     for name, (config, seed, groups) in CASES.items():
         folder = Path(tempfile.mkdtemp())
-        write_random_model(folder, {**config, "eos_token_id": 0}, seed, "float32", name_prefix="transformer.")
+        folder_for_the_reference(folder, config, seed)
         (folder / "tokenizer.json").write_text(json.dumps({
             "version": "1.0", "truncation": None, "padding": None, "added_tokens": [], "normalizer": None,
             "pre_tokenizer": {"type": "Whitespace"}, "post_processor": None, "decoder": None,

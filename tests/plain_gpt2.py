@@ -5,9 +5,11 @@ itself and computes with ordinary tensor arithmetic (float64 by default, so that
 the more exact side of every comparison) on whatever device its weights lie: the CPU
 for the small models, a GPU for a model of the benchmark's full size. Each function cites the
 reference lines its formula comes from. The reference's own model code was run once
-on the CPU against this file (tests/golden/make_golden.py); the two options the
-reference rejects (exact-erf gelu and scaling by inverse layer index,
-damendaemon/config.py:301-303) rest on their formulas alone.
+on the CPU against this file (tests/golden/make_golden.py). The two options the
+reference rejects (damendaemon/config.py:301-303) are held in other ways: scaling by
+inverse layer index against the reference run on weights whose queries carry the
+factor (the "Bscaled" case of make_golden.py), the exact-erf gelu against torch's own
+function in float64 (tests/test_plain_against_golden.py).
 """
 from __future__ import annotations
 

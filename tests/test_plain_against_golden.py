@@ -51,3 +51,14 @@ def test_plain_window_attention():
     # a window query sees exactly itself and the 3 keys before it
     ref = causal_attention(q[5:9], k[5:9], v[5:9], 0.25)
     assert torch.allclose(win[8], ref[3])
+
+
+def test_plain_activations_against_the_library_functions():
+    """The exact-erf gelu, which the reference refuses (damendaemon/config.py:301), and gelu_new, which it computes as
+    F.gelu(u, approximate='tanh') (damendaemon/gpt2.py:63), held to torch's own functions in float64."""
+    from plain_gpt2 import gelu_erf, gelu_new
+    u = torch.cat([torch.linspace(-12, 12, 4001, dtype=torch.float64), torch.tensor([0.0, -0.0, 1e-30, -1e-30, 40.0, -40.0],
+                                                                                     dtype=torch.float64)])
+    assert (gelu_erf(u) - torch.nn.functional.gelu(u, approximate="none")).abs().max() < 1e-14
+    assert (gelu_new(u) - torch.nn.functional.gelu(u, approximate="tanh")).abs().max() < 1e-14
+    assert (gelu_erf(u) - gelu_new(u)).abs().max() > 1e-4          # the two are different functions
