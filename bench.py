@@ -281,7 +281,7 @@ def main():
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     parser.add_argument("--no-graph", action="store_true", help="launch every decode kernel eagerly (for profilers)")
-    parser.add_argument("--kernel-case", help="time one kernel alone at XL shape (see damendaemon_b200/kernel_cases.py)")
+    parser.add_argument("--kernel-case", help="time one kernel alone at XL shape (see bench_kernel_cases.py)")
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
     args = parser.parse_args()
@@ -294,7 +294,7 @@ def main():
         print(json.dumps(run_workload(args.workload)), flush=True)
         return 0
     if args.kernel_case:
-        from damendaemon_b200.kernel_cases import time_case
+        from bench_kernel_cases import time_case
         print(json.dumps(time_case(args.kernel_case, args.case_iters)), flush=True)
         return 0
     if args.warmup < 3:

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from . import kernels as K
+from damendaemon_b200 import kernels as K
 
 H, D, PAGE = 25, 64, 16
 SHAPES = {"qkv": (4800, 1600, "bias"), "proj": (1600, 1600, "residual"), "fc": (6400, 1600, "gelu"),

@@ -52,10 +52,8 @@ struct AttnParams {
     float scale_log2e;
     int new_rows;                   // 1: this step's keys and values are also at hand as rows beside the queries
     int store_new;                  // 1: the kernel itself puts those rows into the cache (every entry starts on a key-block boundary)
-    unsigned long long* timeline;   // null, or 64 time stamps (ns) per block: where a block's time goes
 };
 
-unsigned long long* g_timeline = nullptr;
 
 __device__ __forceinline__ float exp2_approx(float x) {
     float y;
@@ -172,10 +170,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    unsigned long long* stamps = p.timeline ? p.timeline + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 64 : nullptr;
-    if (stamps && threadIdx.x == 0) stamps[0] = tc::global_ns();
     dd_grid_wait();              // queries and the cache are earlier kernels' results
-    if (stamps && threadIdx.x == 0) stamps[1] = tc::global_ns();
 
     if (warp == 0) {
         // ---- TMA ----
@@ -214,7 +209,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     tc::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
                     tc::tma_load_2d(k_dst, &map_k_new, kh * D, row, &kv_full[s]);
                     tc::tma_load_2d(v_dst, &map_v_new, kh * D, row, &kv_full[s]);
-                    if (stamps && j < 8) stamps[56 + j] = tc::global_ns();
                 }
                 continue;
             }
@@ -251,7 +245,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             __syncwarp();
             if (lane == 0) tc::mbar_expect_tx(&kv_full[s], (uint32_t)n_valid * page_bytes);
-            if (stamps && lane == 0 && j < 8) stamps[56 + j] = tc::global_ns();
         }
         if (p.store_new && h % (p.H / p.KH) == 0) {
             // The pair's own keys and values are its last key blocks (one per tile), and they lie in shared memory in
@@ -335,7 +328,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     for (int t = 0; t < TILES; ++t) {
                         if (!(pending & (1u << t)) || !tc::mbar_try_wait(&p_ready[t], added[t] & 1)) continue;
                         tc::fence_after_sync();
-                        if (stamps && j < 8 && t == 0) stamps[40 + 2 * j] = tc::global_ns();
 #pragma unroll
                         for (int k = 0; k < BKV / 16; ++k)
                             tc::mma_bf16_a_tmem(tmem_base + o_col(t), tmem_base + p_col(t) + k * 8,
@@ -351,7 +343,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                 }
                 if (ok) tc::mma_commit(&kv_empty[s]);            // keys and values of this block have been read
-                if (stamps && j < 8) stamps[41 + 2 * j] = tc::global_ns();
             }
         }
     } else if (((warp - 2) >> 2) < n_tiles) {
@@ -373,8 +364,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             alive = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[t], c & 1, abort_flag));
             if (!alive) break;
             tc::fence_after_sync();
-            const bool stamp = stamps && threadIdx.x == 64 && c < 8;
-            if (stamp) stamps[8 + 4 * c] = tc::global_ns();
             // the row's 128 scores of the block into registers: four loads in flight, one wait; then the columns are free
             uint32_t sv[BKV];
 #pragma unroll
@@ -393,7 +382,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int i = 0; i < BKV; i += 2)
                 mx4[(i >> 1) & 3] = max_of_three(mx4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            if (stamp) stamps[9 + 4 * c] = tc::global_ns();
             const float m_true = fmaxf(m, mx * p.scale_log2e);     // the scale is positive
             const bool move = m_true > m + 8.f || (m == -CUDART_INF_F && m_true != -CUDART_INF_F);
             const float alpha = move ? exp2_approx(m - m_true) : 1.f;      // 0 from -inf
@@ -459,8 +447,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc::fence_before_sync();          // this thread's TMEM reads and writes are done
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&p_ready[t]);
-            if (stamp) stamps[10 + 4 * c] = tc::global_ns();
-            if (stamps && threadIdx.x == 64 + BQ && c < 8) stamps[11 + 4 * c] = tc::global_ns();
         }
         // the output row after the last block's P.V
         if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (j_last - j_first) & 1, abort_flag));
@@ -528,11 +514,6 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long rows, int co
 }
 }  // namespace
 
-// Debugging aid: a device buffer of 64 time stamps (ns) per block of the next launches, null switches it off:
-// 0 start, 1 inputs ready; for the first eight key blocks j of the lower tile: 8+4j scores there, 9+4j maximum known,
-// 10+4j P handed over (thread 64), 11+4j P of the upper tile's j-th block handed over; 40+2j the lower tile's P seen by
-// the MMA thread, 41+2j the block's P.V products issued; 56+j loads issued.
-DD_API void dd_attention_prefill_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
 
 // Head size 64, pages of 8, 16, 32, 64 or 128 tokens (a page is one TMA box inside a 128-key block).
 DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, int head_dim, int page_size, int dtype) {
@@ -586,7 +567,6 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.out = (__nv_bfloat16*)out; p.error_flag = error_flag;
     p.n_entries = n_entries; p.max_blocks = max_blocks; p.out_stride = out_stride; p.H = n_heads; p.KH = n_kv_heads;
     p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
-    p.timeline = g_timeline;
     p.new_rows = k_new != nullptr;
     p.store_new = store_new != 0;
     // an upper bound of the number of pairs of 128-row tiles; blocks beyond the real count return at once

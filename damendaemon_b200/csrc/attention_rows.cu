@@ -177,6 +177,9 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
                 int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale, int n_splits,
                 int* error_flag, cudaStream_t s) {
     const long long items = (long long)n_tokens * H * n_splits;
+    if ((items + WARPS - 1) / WARPS > 0x7fffffffLL)
+        return dd_fail("dd_attention_rows: %d tokens x %d heads x %d splits are more work items than one launch takes",
+                       n_tokens, H, n_splits);
     const int grid = dd_ceil_div(items, WARPS);
     const size_t smem = (size_t)WARPS * d * sizeof(float);
 #define DD_ROWS(DPL)                                                                                        \

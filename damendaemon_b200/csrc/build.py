@@ -32,7 +32,7 @@ LIBRARIES = {
     "core": ["errors.cu", "embed.cu", "layernorm.cu", "gemm_simt.cu", "kv_store.cu", "attention_rows.cu",
              "sampling.cu"],
     "tensor": ["errors.cu", "gemm_tcgen05.cu", "attention_decode.cu", "attention_decode_pages.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu",
-               "mlp_decode.cu"],
+               "wait_probe.cu"],
 }
 HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -82,8 +82,18 @@ def build_dir() -> Path:
         return local
     except OSError:
         pass
+    # A shared temporary directory: the folder's name can be guessed, so it is taken only if it is ours alone
+    # (made by this user, closed to group and others); a library found in somebody else's folder is never loaded.
     fallback = Path(tempfile.gettempdir()) / f"damendaemon_b200_build_{os.getuid()}"
-    fallback.mkdir(parents=True, exist_ok=True)
+    try:
+        fallback.mkdir(mode=0o700)
+    except FileExistsError:
+        pass
+    info = fallback.lstat()
+    import stat
+    if not stat.S_ISDIR(info.st_mode) or info.st_uid != os.getuid() or info.st_mode & 0o022:
+        raise BuildError(f"{fallback} exists but is not a folder that only user {os.getuid()} can write; "
+                         "remove it, or make the package's csrc/_build folder writable")
     return fallback
 
 

@@ -55,10 +55,8 @@ struct GemmParams {
     int vec;                     // out, residual and bias allow 16-byte accesses at every row start (tiles of 128 tokens)
     const uint8_t* prefetch;        // null, or memory a later kernel will stream (the next weight matrix):
     unsigned long long prefetch_bytes;   // every block asks L2 to fetch its share while this kernel runs
-    unsigned long long* timeline;   // null, or 8 time stamps (ns) per block for looking at where a block's time goes
 };
 
-unsigned long long* g_timeline = nullptr;
 
 template <int BN> struct Config {
     static constexpr bool BY_TOKEN = BN >= 128;      // accumulator lanes are tokens (else output features)
@@ -392,7 +390,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // the epilogue must have drained this accumulator (passes at once the first two times)
                 if (!tc::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1) ^ 1, abort_flag)) break;
                 tc::fence_after_sync();
-                if (p.timeline && local < 3) p.timeline[blockIdx.x * 16 + 1 + 4 * local] = tc::global_ns();
                 const uint32_t tmem_d = tmem_base + acc * C::ACC_COLS;
                 for (int i = 0; i < n_kblocks; ++i, ++it) {
                     const int s = it % C::STAGES;
@@ -409,13 +406,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     tc::mma_commit(&empty_bar[s]);     // the stage is free once these MMAs have read it
                 }
-                if (p.timeline && local < 3) p.timeline[blockIdx.x * 16 + 2 + 4 * local] = tc::global_ns();
                 if (ok) tc::mma_commit(&tmem_full_bar[acc]);   // the accumulator is complete
             }
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. 32*(w%4)+31
-        if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 16] = tc::global_ns();
         dd_grid_wait();              // bias is constant, but residual, workspace and counters are earlier kernels' data
         const int quarter = warp & 3;
         // the two warps of a lane quarter split the tile's columns in halves (in chunks of 16)
@@ -435,7 +430,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*epilogue_abort) break;                   // the same decision in all eight warps
             tc::fence_after_sync();
-            if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 3 + 4 * local] = tc::global_ns();
             const uint32_t lane_addr = tmem_base + acc * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             if (c_begin >= c_limit || b0 + c_begin >= rows_b) {      // no columns for this warp in this tile
                 tc::fence_before_sync();
@@ -469,7 +463,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
-                if (p.timeline && threadIdx.x == 64 && local < 3) p.timeline[blockIdx.x * 16 + 4 + 4 * local] = tc::global_ns();
             } else if (!BY_TOKEN) {
                 // partial sums to the workspace, then the last block of this tile reduces
                 const int n = row, m0 = b0;
@@ -732,7 +725,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     // neighbouring features, so both the remote writes and the reads below walk consecutive banks
     float* reduce_buf = reinterpret_cast<float*>(tiles + C::STAGES * C::STAGE_BYTES + 256);
 
-    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 0] = tc::global_ns();
     dd_launch_dependents();      // the next kernel may begin its own set-up (and ask for its weights) at once
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = (int)tc::cluster_size();
@@ -764,7 +756,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 1] = tc::global_ns();
     tc::cluster_arrive();        // "my shared memory exists": waited for before the first remote write
 
     if (warp == 0) {
@@ -779,7 +770,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
             }
             prefetch_share(p);
             dd_grid_wait();
-            if (p.timeline) p.timeline[blockIdx.x * 8 + 2] = tc::global_ns();
             for (int i = 0; i < n_kblocks; ++i) {
                 const int s = i % C::STAGES;
                 uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
@@ -803,7 +793,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 const int s = i % C::STAGES;
                 const uint32_t phase = (i / C::STAGES) & 1;
                 if (!tc::mbar_wait(&full_bar[s], phase, abort_flag)) { ok = false; break; }
-                if (p.timeline && i == 0) p.timeline[blockIdx.x * 8 + 3] = tc::global_ns();
                 tc::fence_after_sync();
                 const uint32_t a_addr = tc::smem_u32(tiles + s * C::STAGE_BYTES);
                 const uint32_t b_addr = a_addr + C::A_BYTES;
@@ -815,7 +804,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 }
                 tc::mma_commit(&empty_bar[s]);
             }
-            if (p.timeline) p.timeline[blockIdx.x * 8 + 4] = tc::global_ns();
             if (ok) tc::mma_commit(tmem_full_bar);
         }
     }
@@ -834,7 +822,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         }
         const bool have = n_kblocks > 0 && tc::mbar_wait(tmem_full_bar, 0, abort_flag);
         tc::fence_after_sync();
-        if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 5] = tc::global_ns();
         const int owner = f / slice, lf = f - owner * slice;
         // my partial row of feature f goes to the block that owns f
         const uint32_t remote = tc::map_to_rank(reduce_buf + (size_t)rank * BN * slice + lf, (uint32_t)owner);
@@ -854,7 +841,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     __syncwarp();
     tc::cluster_arrive();
     tc::cluster_wait();          // all partial rows have landed
-    if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 6] = tc::global_ns();
 
     if (warp >= 2) {
         dd_grid_wait();          // residual is an earlier kernel's data
@@ -892,7 +878,6 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 8 + 7] = tc::global_ns();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_flag, 8);
     if (warp == 1) {
         tc::fence_after_sync();
@@ -1021,10 +1006,6 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
 
 }  // namespace
 
-// Debugging aid: a device buffer of time stamps (ns) that the kernels fill, null switches it off: 8 per block from
-// the cluster kernel; 16 per block from the persistent kernel (0 start, then for the first three tiles: MMAs begin,
-// MMAs issued, epilogue begins, epilogue done).
-DD_API void dd_gemm_tcgen05_timeline(unsigned long long* buffer) { g_timeline = buffer; }
 
 // Chooses the token tile, the K split and how the split is reduced (*cluster = 1: inside a thread-block
 // cluster over distributed shared memory; 0: through a global workspace). Returns splits (>= 1).
@@ -1115,7 +1096,6 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     GemmParams p;
     p.bias = bias; p.residual = residual; p.out = out; p.workspace = workspace; p.counters = counters;
     p.error_flag = error_flag; p.M = M; p.N = N; p.K = K; p.ldr = ldr; p.ldo = ldo; p.act = act; p.out_dtype = out_dtype;
-    p.timeline = g_timeline;
     p.prefetch = (const uint8_t*)prefetch;
     p.prefetch_bytes = (prefetch && prefetch_bytes > 0 && !((uintptr_t)prefetch & 15)) ? (unsigned long long)prefetch_bytes : 0;
     p.splits = splits; p.kblocks_per_split = dd_ceil_div(kblocks, splits);

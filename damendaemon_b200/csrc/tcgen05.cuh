@@ -55,14 +55,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false if the phase did not complete within the limit (or another thread
-// of the block has already given up: *abort != 0).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+// of the block has already given up: *abort != 0). The kernels wait with the default
+// limit; a shorter one is for the probe that shows a wait giving up (wait_probe.cu).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = global_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ff) == 0) {
-            if (*abort || global_ns() - start > WAIT_LIMIT_NS) {
+            if (*abort || global_ns() - start > limit_ns) {
                 *abort = 1;
                 return false;
             }

@@ -38,8 +38,7 @@ _SIGNATURES = {
     },
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
-        "dd_mlp_decode": [_c_void, _c_int, _c_void, _c_void, _c_float, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void,
-                          _c_void] + [_c_int] * 5 + [_c_void, _c_void],
+        "dd_wait_probe": [ctypes.c_ulonglong, _c_void, _c_void, _c_void],
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
@@ -160,6 +159,15 @@ def read_error_flag(device):
     if value:
         flag.zero_()
     return value
+
+
+def wait_probe(limit_ns, device):
+    """Launch the block whose barrier nobody arrives at (csrc/wait_probe.cu) with a wait limit of limit_ns and
+    return how long its two waiting warps waited, in ns. The device's error word then has bit 8 set, as after a
+    wait that ran out in a pipelined kernel; read_error_flag reads and clears it."""
+    waited = torch.zeros(2, dtype=torch.int64, device=device)
+    _call(library("tensor"), "dd_wait_probe", int(limit_ns), _ptr(error_flag(device)), waited.data_ptr(), _stream())
+    return waited.tolist()
 
 
 # ---------------------------------------------------------------- kernels
@@ -434,39 +442,3 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
           n_heads, kv_heads, head_dim, page_size, n_pages, 0 if window is None else int(window), float(scale),
           _ptr(error_flag(q.device)), _stream())
     return out
-
-
-_mlp_scratch = {}
-
-
-def mlp_decode_scratch(tokens, width, inner, device):
-    """Floats of scratch the fused decode feed-forward needs for this problem; 0 if it does not take it."""
-    lib = library("tensor")
-    lib.dd_mlp_decode_scratch.argtypes, lib.dd_mlp_decode_scratch.restype = [_c_int] * 4, ctypes.c_longlong
-    return int(lib.dd_mlp_decode_scratch(tokens, width, inner, sm_count(device)))
-
-
-def mlp_decode(x, gamma, beta, eps, w_up, b_up, w_down, b_down, activation):
-    """x += w_down @ act(w_up @ layernorm(x) + b_up) + b_down in one kernel, for up to 16 rows of the float32
-    residual stream x (in place). w_up [inner, width], w_down [width, inner] bfloat16. Returns x, or None if
-    the kernel does not take the sizes."""
-    _rows(x, "x"), _rows(w_up, "w_up"), _rows(w_down, "w_down")
-    tokens, width = x.shape
-    inner = w_up.shape[0]
-    if w_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16 or w_up.shape[1] != width or w_down.shape != (width, inner):
-        raise KernelError("mlp_decode: needs bfloat16 w_up [inner, width] and w_down [width, inner]")
-    need = mlp_decode_scratch(tokens, width, inner, x.device)
-    if need == 0:
-        return None
-    key = torch.device(x.device).index or 0
-    state = _mlp_scratch.get(key)
-    if state is None or state[0].numel() < need:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("mlp_decode scratch must exist before a graph capture (run the step once eagerly)")
-        state = _mlp_scratch[key] = (torch.empty(need, dtype=torch.float32, device=x.device),
-                                     torch.zeros(2, dtype=torch.int32, device=x.device))
-    _call(library("tensor"), "dd_mlp_decode", _ptr(x, "x", torch.float32), x.stride(0), _ptr(gamma, "gamma", torch.float32),
-          _ptr(beta, "beta", torch.float32), float(eps), _ptr(w_up, "w_up"), w_up.stride(0), _ptr(b_up, "b_up", torch.float32),
-          _ptr(w_down, "w_down"), w_down.stride(0), _ptr(b_down, "b_down", torch.float32), _ptr(state[0]), _ptr(state[1]),
-          tokens, width, inner, ACTIVATIONS[activation], sm_count(x.device), _ptr(error_flag(x.device)), _stream())
-    return x

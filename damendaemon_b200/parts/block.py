@@ -14,9 +14,4 @@ class PreNormBlock:
 
     def forward(self, x, ctx, cache, position):
         x = self.mixer.forward(self.norm1.forward(x), x, ctx, cache, position)
-        fused = getattr(self.feed_forward, "forward_normed", None)
-        if fused is not None:
-            out = fused(self.norm2, x, ctx)          # a feed-forward may offer to apply the norm before it itself
-            if out is not None:
-                return out
         return self.feed_forward.forward(self.norm2.forward(x), x, ctx)

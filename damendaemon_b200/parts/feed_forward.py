@@ -2,8 +2,6 @@
 epilogue and the residual add into the second's (damendaemon/gpt2.py:62-64)."""
 from __future__ import annotations
 
-import torch
-
 from .interfaces import FeedForward
 from .linear import linear
 from .registry import register_feed_forward
@@ -34,19 +32,6 @@ class DenseFeedForward(FeedForward):
         if spec.down_bias:
             decls.append(TensorDecl(spec.down_bias, (spec.width,), "vector"))
         return decls
-
-    def forward_normed(self, norm, x, ctx):
-        """Optional fast path: apply ``norm`` and this feed-forward to the residual stream x in one kernel.
-        Returns the updated stream, or None when the fused kernel does not take the case (then the caller
-        runs the norm and ``forward`` as usual). Taken for bfloat16 decode steps of up to 16 tokens after
-        a LayerNorm: three launches become one."""
-        from .. import kernels
-        from .norms import LayerNorm
-        if self.runtime.gemm == "simt" or x.dtype != torch.float32 or self.up_w.dtype != torch.bfloat16 \
-                or not isinstance(norm, LayerNorm) or x.shape[0] > 16 or not self.runtime.fuse:
-            return None
-        return kernels.mlp_decode(x, norm.gamma, norm.beta, norm.spec.eps, self.up_w, self.up_b, self.down_w, self.down_b,
-                                  self.spec.activation)
 
     def forward(self, y, residual, ctx):
         hidden = linear(self.runtime, y, self.up_w, self.up_b, activation=self.spec.activation)

@@ -19,8 +19,7 @@ PositionEncoding  tensor_decls(spec); embedding_table() -> table or None (added 
                   for encodings that rotate or bias inside the mixer
 Mixer             tensor_decls(spec); cache_needs(spec) -> [PagedKeyValues | RequestState];
                   forward(y, residual, ctx, cache, position) -> residual + mix(y)   (float32 [N,width])
-FeedForward       tensor_decls(spec); forward(y, residual, ctx) -> residual + ff(y); optionally
-                  forward_normed(norm, x, ctx) -> x + ff(norm(x)) or None (a fused norm + feed-forward)
+FeedForward       tensor_decls(spec); forward(y, residual, ctx) -> residual + ff(y)
 Arrangement       cls(layer_spec, norm1, mixer, norm2, feed_forward);
                   forward(x, ctx, cache, position) -> x
 
@@ -40,8 +39,6 @@ class Runtime:
     device: torch.device
     gemm: str = "auto"            # 'auto' | 'simt' | 'tcgen05'
     attention: str = "auto"       # 'auto' | 'mma' (no tcgen05 prompt kernel) | 'rows' (the general kernel only)
-    fuse: bool = False            # let parts take their fused multi-part kernels (decode feed-forward with its norm:
-                                  # measured slower than the separate kernels on B200 so far, hence off)
 
 
 class Part:

@@ -158,3 +158,23 @@ def test_strided_views_and_refusals(K):
         K.gemm_tcgen05(a[:, :100].contiguous(), w[:, :100].contiguous())
     with pytest.raises(K.KernelError, match="bfloat16"):
         K.gemm_tcgen05(a.float(), w.float())
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_goes_on(K):
+    """A barrier at which nobody arrives, waited on through the function every pipeline of the library waits with,
+    under a limit of 2 ms: the wait gives up, the kernel returns, bit 8 stands in the error word, a second waiting warp
+    leaves through the block's abort flag well before its own limit, and a product right after it is correct."""
+    assert K.read_error_flag(DEV) == 0
+    limit = 2_000_000
+    first, second = K.wait_probe(limit, DEV)
+    torch.cuda.synchronize()
+    assert K.read_error_flag(DEV) == 8
+    assert limit <= first < 50 * limit, f"the first warp gave up after {first} ns"
+    assert 0 < second < 5 * limit, f"the second warp left after {second} ns, not with the block's abort flag"
+    assert K.read_error_flag(DEV) == 0          # reading cleared it
+    a, w, bias, res = operands(8, 1600, 1600, seed=3)
+    out = K.gemm_tcgen05(a, w, out_dtype=torch.float32)
+    assert (out.double() - a.double() @ w.double().t()).abs().max().item() < 2e-4 * math.sqrt(1600 / 64)
+    assert K.read_error_flag(DEV) == 0
+    with pytest.raises(K.KernelError):
+        K.wait_probe(2_000_000_000, DEV)        # limits beyond a second are refused

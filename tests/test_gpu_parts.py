@@ -256,39 +256,3 @@ def test_bfloat16_width_that_is_no_multiple_of_8():
     w = torch.randn(36, 100, generator=g).to(torch.bfloat16).to(DEV)
     out = linear(runtime(torch.bfloat16), a, w, out_dtype=torch.float32)
     assert (out.double() - a.double() @ w.double().t()).abs().max() < 1e-3
-
-
-@pytest.mark.parametrize("activation", ["gelu_new", "gelu"])
-@pytest.mark.parametrize("tokens,width,inner", [(1, 1600, 6400), (8, 1600, 6400), (16, 192, 400), (5, 96, 320), (3, 64, 256)])
-def test_fused_decode_feed_forward(tokens, width, inner, activation):
-    """LayerNorm + up projection + activation + down projection + residual add in one kernel against the plain functions,
-    twice in a row (the grid barrier's counters must be left at zero)."""
-    from damendaemon_b200 import kernels
-    from damendaemon_b200.parts.feed_forward import DenseFeedForward
-    from damendaemon_b200.parts.norms import LayerNorm
-    g = torch.Generator().manual_seed(11)
-    raw = {"up.w": (torch.randn(width, inner, generator=g) * width ** -0.5).to(torch.bfloat16).float(), "up.b": torch.randn(inner, generator=g) * 0.1,
-           "down.w": (torch.randn(inner, width, generator=g) * inner ** -0.5).to(torch.bfloat16).float(), "down.b": torch.randn(width, generator=g) * 0.1,
-           "n.w": 1 + 0.1 * torch.randn(width, generator=g), "n.b": 0.1 * torch.randn(width, generator=g)}
-    spec = DenseFeedForwardSpec("dense", width, inner, activation, "up.w", "up.b", "down.w", "down.b", stored_in_out=True)
-    placed = {k: (v.t().contiguous().to(torch.bfloat16) if v.dim() == 2 else v).to(DEV) for k, v in raw.items()}
-    rt = Runtime(dtype=torch.bfloat16, device=DEV, fuse=True)
-    ff = DenseFeedForward(spec, placed, rt)
-    norm = LayerNorm(NormSpec("layernorm", width, 1e-5, "n.w", "n.b"), placed, rt)
-    assert DenseFeedForward(spec, placed, runtime(torch.bfloat16)).forward_normed(norm, torch.zeros(2, width, device=DEV), None) is None
-    x = torch.randn(tokens, width, generator=g) * 2 + 0.5
-    y = plain.layer_norm(x.double(), raw["n.w"].double(), raw["n.b"].double(), 1e-5)
-    u = y @ raw["up.w"].double() + raw["up.b"].double()
-    act = plain.gelu_new(u) if activation == "gelu_new" else plain.gelu_erf(u)
-    want = x.double() + act @ raw["down.w"].double() + raw["down.b"].double()
-    bound = 3 * 2.0 ** -8 * float(want.abs().max())
-    for _ in range(2):
-        stream = x.to(DEV).clone()
-        got = ff.forward_normed(norm, stream, None)
-        assert got is not None and got.data_ptr() == stream.data_ptr()
-        assert kernels.read_error_flag(DEV) == 0
-        assert (got.double().cpu() - want).abs().max() < bound
-    # and it agrees with the unfused path
-    unfused = ff.forward(norm.forward(x.to(DEV)), x.to(DEV).clone(), None)
-    assert (unfused - got).abs().max() < bound
-    assert ff.forward_normed(norm, torch.zeros(17, width, device=DEV), None) is None      # more than 16 tokens: not taken
