@@ -283,6 +283,7 @@ def main():
     parser.add_argument("--no-graph", action="store_true", help="launch every decode kernel eagerly (for profilers)")
     parser.add_argument("--kernel-case", help="time one kernel alone at XL shape (see bench_kernel_cases.py)")
     parser.add_argument("--case-iters", type=int, default=50)
+    parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
     args = parser.parse_args()
     if args.gpus != 1:
@@ -295,7 +296,7 @@ def main():
         return 0
     if args.kernel_case:
         from bench_kernel_cases import time_case
-        print(json.dumps(time_case(args.kernel_case, args.case_iters)), flush=True)
+        print(json.dumps(time_case(args.kernel_case, args.case_iters, graph=args.case_graph)), flush=True)
         return 0
     if args.warmup < 3:
         args.warmup = 3

@@ -95,17 +95,30 @@ def build(name, device="cuda:0"):
     raise ValueError(f"unknown kernel case {name!r}")
 
 
-def time_case(name, iters=50, device="cuda:0"):
+def time_case(name, iters=50, device="cuda:0", graph=False):
+    """graph: the launches are captured into one CUDA graph and replayed, so that the host's time per launch (a
+    few microseconds of Python) does not stand between two kernels, as it does not in a captured decode step."""
     run, work = build(name, device)
     for i in range(3):
         run(i)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(iters):
-        run(i)
-    stop.record()
+    if graph:
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            for i in range(iters):
+                run(i)
+        captured.replay()
+        torch.cuda.synchronize()
+        start.record()
+        captured.replay()
+        stop.record()
+    else:
+        start.record()
+        for i in range(iters):
+            run(i)
+        stop.record()
     torch.cuda.synchronize()
     us = start.elapsed_time(stop) * 1000.0 / iters
     return {"case": name, "us_per_launch": round(us, 2), "GB_per_s": round(work["bytes"] / us / 1e3, 1),
-            "TFLOP_per_s": round(work["flops"] / us / 1e6, 1), "iters": iters}
+            "TFLOP_per_s": round(work["flops"] / us / 1e6, 1), "iters": iters, "graph": bool(graph)}

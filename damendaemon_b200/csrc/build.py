@@ -32,7 +32,7 @@ LIBRARIES = {
     "core": ["errors.cu", "embed.cu", "layernorm.cu", "gemm_simt.cu", "kv_store.cu", "attention_rows.cu",
              "sampling.cu"],
     "tensor": ["errors.cu", "gemm_tcgen05.cu", "attention_decode.cu", "attention_decode_pages.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu",
-               "wait_probe.cu", "decode_chain.cu"],
+               "wait_probe.cu"],
 }
 HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -51,7 +51,7 @@ def require_cuda(device):
 class Engine:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", kv_tokens=None,
                  page_size=16, max_requests=64, device="cuda:0", gemm="auto", check_device_errors=True,
-                 use_graph=False, chain=True):
+                 use_graph=False):
         """Either ``model_dir`` (config.json + model.safetensors) or ``config`` (the raw
         config.json dict) with ``tensors`` ({checkpoint name: tensor})."""
         self.device = require_cuda(device)
@@ -69,7 +69,7 @@ class Engine:
             weights = load_weights(model_dir, self.spec, decls, self.dtype, self.device)
         else:
             weights = check_and_place(DictSource(tensors), self.spec, decls, self.dtype, self.device)
-        self.runtime = Runtime(dtype=self.dtype, device=self.device, gemm=gemm, chain=chain)
+        self.runtime = Runtime(dtype=self.dtype, device=self.device, gemm=gemm)
         kernels.library("core")
         if self.dtype == torch.bfloat16 and gemm != "simt":
             kernels.library("tensor")
@@ -99,7 +99,6 @@ class Engine:
         if self.dtype == torch.bfloat16 and gemm != "simt":
             heads = max((getattr(l.mixer, "n_heads", 1) for l in self.spec.layers), default=1)
             kernels._tile_counters(self.device, max(8192, max_requests * heads))
-            kernels.chain_barrier(self.device)
         self._meta_dev = None
         self._meta_host = []
         self._meta_events = []

@@ -39,7 +39,6 @@ _SIGNATURES = {
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
         "dd_wait_probe": [ctypes.c_ulonglong, _c_void, _c_void, _c_void],
-        "dd_decode_chain": [_c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_void],
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
@@ -101,8 +100,6 @@ _pdl = True
 
 def _call(lib, fn, *args, n_kernels=1):
     global launches
-    if _pending:
-        flush_chain()            # deferred products and norms run before anything that may read their results
     launches += n_kernels
     code = getattr(lib, fn)(*args)
     if code:
@@ -161,122 +158,7 @@ def read_error_flag(device):
     value = int(flag.item())
     if value:
         flag.zero_()
-        key = torch.device(device).index or 0
-        if value & 8 and key in _chain_barriers:
-            _chain_barriers[key].zero_()         # blocks that gave up at a chain's barrier left their arrivals behind
     return value
-
-
-# ---------------------------------------------------------------- chains of small products in one kernel
-
-class DdChainPhase(ctypes.Structure):
-    _fields_ = [(name, ctypes.c_void_p) for name in ("w", "bias", "input", "norm_src", "gamma", "beta", "norm_out", "out",
-                                                     "residual")] + [("eps", ctypes.c_float)] + \
-               [(name, ctypes.c_int) for name in ("N", "K", "ldw", "ld_in", "ld_norm", "ld_out", "ld_res", "act", "out_f32")]
-
-
-CHAIN_TOKENS = 8          # a step of at most this many tokens may run its products and norms as chains
-CHAIN_MAX_PHASES = 4
-_chain_open = False
-_pending = []
-_chain_barriers = {}
-chains_launched = 0
-
-
-def chain_takes(M, N, K):
-    """Can a product of these sizes be a phase of a chain (csrc/decode_chain.cu)?"""
-    return 1 <= M <= CHAIN_TOKENS and N > 0 and K > 0 and N % 8 == 0 and K % 32 == 0 and K <= 12288
-
-
-def chain_barrier(device):
-    """The two words of the chains' grid barrier on this device (allocated before any graph capture)."""
-    key = torch.device(device).index or 0
-    if key not in _chain_barriers:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the chain barrier must exist before a graph capture (kernels.chain_barrier)")
-        _chain_barriers[key] = torch.zeros(2, dtype=torch.int32, device=device)
-    return _chain_barriers[key]
-
-
-class chain:
-    """While open, ``layernorm`` and ``gemm_tcgen05`` calls on at most CHAIN_TOKENS rows that the chain kernel takes
-    are not launched but noted, each returning its output tensor as always; the notes are launched, in order, as
-    few kernels as possible (a norm and the product that reads it are one phase; up to CHAIN_MAX_PHASES phases are
-    one kernel with grid barriers between them) as soon as any other kernel of this module is called, and when
-    the chain closes. Only for code that touches its tensors through this module's kernels alone: a torch operation
-    on a deferred result would read it before it was computed."""
-
-    def __enter__(self):
-        global _chain_open
-        self.was_open, _chain_open = _chain_open, True
-        return self
-
-    def __exit__(self, *exc):
-        global _chain_open
-        _chain_open = self.was_open
-        if exc[0] is None:
-            flush_chain()
-        else:
-            _pending.clear()
-        return False
-
-
-def flush_chain():
-    global _chain_open
-    if not _pending:
-        return
-    ops = list(_pending)
-    _pending.clear()
-    was_open, _chain_open = _chain_open, False          # what is launched from here on is launched for real
-    try:
-        phases, i = [], 0
-        while i < len(ops):
-            op = ops[i]
-            if op[0] == "norm":
-                nxt = ops[i + 1] if i + 1 < len(ops) else None
-                if nxt is not None and nxt[0] == "linear" and nxt[1] is op[5]:
-                    phases.append((op, nxt))
-                    i += 2
-                else:
-                    _launch_chain(phases)
-                    phases = []
-                    _, x, gamma, beta, eps, out = op
-                    layernorm(x, gamma, beta, eps, out.dtype, out=out)
-                    i += 1
-            else:
-                phases.append((None, op))
-                i += 1
-            if len(phases) == CHAIN_MAX_PHASES:
-                _launch_chain(phases)
-                phases = []
-        _launch_chain(phases)
-    finally:
-        _chain_open = was_open
-
-
-def _launch_chain(phases):
-    global chains_launched
-    if not phases:
-        return
-    array = (DdChainPhase * len(phases))()
-    M = None
-    for slot, (norm, linear) in zip(array, phases):
-        _, a, w, bias, residual, activation, out = linear
-        M = a.shape[0]
-        slot.w, slot.bias, slot.out, slot.residual = _ptr(w, "w"), _ptr(bias, "bias"), _ptr(out, "out"), _ptr(residual, "residual")
-        slot.N, slot.K, slot.ldw, slot.ld_out = w.shape[0], w.shape[1], w.stride(0), out.stride(0)
-        slot.ld_res = 0 if residual is None else residual.stride(0)
-        slot.act, slot.out_f32 = ACTIVATIONS[activation], int(out.dtype == torch.float32)
-        if norm is None:
-            slot.input, slot.ld_in = _ptr(a, "a"), a.stride(0)
-        else:
-            _, x, gamma, beta, eps, normed = norm
-            slot.norm_src, slot.ld_norm, slot.gamma, slot.beta = _ptr(x, "x"), x.stride(0), _ptr(gamma, "gamma"), _ptr(beta, "beta")
-            slot.eps, slot.norm_out = eps, _ptr(normed, "normed")
-    device = phases[0][1][1].device
-    chains_launched += 1
-    _call(library("tensor"), "dd_decode_chain", ctypes.addressof(array), len(phases), M, _ptr(chain_barrier(device)),
-          sm_count(device), _ptr(error_flag(device)), _stream())
 
 
 def wait_probe(limit_ns, device):
@@ -311,10 +193,6 @@ def layernorm(x, gamma, beta, eps, out_dtype, row_index=None, out=None):
         raise KernelError("layernorm input must be contiguous")
     if out is None:
         out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
-    if _chain_open and row_index is None and out_dtype == torch.bfloat16 and x.dtype == torch.float32 and \
-            gamma.dtype == torch.float32 and chain_takes(rows, 8, width):
-        _pending.append(("norm", x, gamma, beta, float(eps), out))
-        return out
     _call(library("core"), "dd_layernorm", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32),
           _ptr(gamma, "gamma", torch.float32), _ptr(beta, "beta", torch.float32), _ptr(out, "out", out_dtype),
           rows, width, float(eps), _dt(out_dtype), _stream())
@@ -445,11 +323,6 @@ def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     _rows(out, "out")
     lib = library("tensor")
-    if _chain_open and splits is None and token_tile is None and cluster is None and prefetch is None and \
-            chain_takes(M, N, K) and w.stride(0) % 8 == 0 and a.stride(0) % 8 == 0 and \
-            (bias is None or bias.dtype == torch.float32) and (residual is None or residual.dtype == torch.float32):
-        _pending.append(("linear", a, w, bias, residual, activation, out))
-        return out
     plan = _plans.get((M, N, K))
     if plan is None:
         tile, mode = ctypes.c_int(0), ctypes.c_int(0)

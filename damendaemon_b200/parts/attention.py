@@ -17,7 +17,6 @@ from .spec import TensorDecl
 @register_mixer("attention")
 class Attention(Mixer):
     graph_safe = True
-    kernels_only = True
 
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime

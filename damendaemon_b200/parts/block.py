@@ -9,8 +9,6 @@ from .registry import register_arrangement
 
 @register_arrangement("pre_norm")
 class PreNormBlock:
-    kernels_only = True
-
     def __init__(self, spec, norm1, mixer, norm2, feed_forward):
         self.spec, self.norm1, self.mixer, self.norm2, self.feed_forward = spec, norm1, mixer, norm2, feed_forward
 

@@ -13,7 +13,6 @@ ACTIVATIONS = ("gelu_new", "gelu")
 @register_feed_forward("dense")
 class DenseFeedForward(FeedForward):
     graph_safe = True
-    kernels_only = True
 
     def __init__(self, spec, weights, runtime):
         if spec.activation not in ACTIVATIONS:

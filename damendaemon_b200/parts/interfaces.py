@@ -39,14 +39,9 @@ class Runtime:
     device: torch.device
     gemm: str = "auto"            # 'auto' | 'simt' | 'tcgen05'
     attention: str = "auto"       # 'auto' | 'mma' (no tcgen05 prompt kernel) | 'rows' (the general kernel only)
-    chain: bool = True            # steps of a few tokens run their products and norms as chains (kernels.chain)
 
 
 class Part:
-    # True if the part reads and writes its tensors through the kernels module alone (no torch arithmetic on
-    # them): its norm and product launches may then be deferred and fused into chains (kernels.chain).
-    kernels_only = False
-
     @staticmethod
     def tensor_decls(spec):
         return []

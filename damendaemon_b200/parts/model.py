@@ -1,8 +1,6 @@
 """A decoder assembled from parts according to a ModelSpec. Architecture-agnostic."""
 from __future__ import annotations
 
-import contextlib
-
 import torch
 
 from .. import kernels
@@ -65,25 +63,17 @@ class DecoderModel:
         self.final_norm = lookup(NORMS, spec.final_norm, "norm")(spec.final_norm, weights, runtime)
         self.graph_safe = all(getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
                               for b in self.blocks)
-        # every part reaches its tensors through the kernels module alone: small steps may then defer their products
-        # and norms and run them as chains (kernels.chain)
-        parts = [self.position, self.final_norm] + [part for b in self.blocks
-                                                    for part in (b, b.norm1, b.mixer, b.norm2, b.feed_forward)]
-        self.kernels_only = all(getattr(part, "kernels_only", False) for part in parts)
 
     def forward(self, ctx, caches):
         """Run the step's tokens; float32 logits [wanted rows, vocab] (or None if none are wanted).
 
         caches: per stop of the run order, the LayerCache view its mixer reads (and writes, if it is its own).
         """
-        chained = self.kernels_only and self.runtime.chain and self.runtime.dtype == torch.bfloat16 and \
-            self.runtime.gemm != "simt" and ctx.n_tokens <= kernels.CHAIN_TOKENS
-        with kernels.chain() if chained else contextlib.nullcontext():
-            x = kernels.embed(ctx.token_ids, ctx.positions, self.token_table, self.position.embedding_table())
-            x = self.position.on_embedding(x, ctx)
-            for stop, entry in enumerate(self.spec.run_order):
-                x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
-            if ctx.n_wanted == 0:
-                return None
-            y = self.final_norm.forward(x, row_index=ctx.want_rows)
-            return linear(self.runtime, y, self.head, out_dtype=torch.float32)
+        x = kernels.embed(ctx.token_ids, ctx.positions, self.token_table, self.position.embedding_table())
+        x = self.position.on_embedding(x, ctx)
+        for stop, entry in enumerate(self.spec.run_order):
+            x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
+        if ctx.n_wanted == 0:
+            return None
+        y = self.final_norm.forward(x, row_index=ctx.want_rows)
+        return linear(self.runtime, y, self.head, out_dtype=torch.float32)

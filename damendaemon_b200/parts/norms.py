@@ -9,8 +9,6 @@ from .spec import TensorDecl
 
 @register_norm("layernorm")
 class LayerNorm(Norm):
-    kernels_only = True
-
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
         self.gamma = weights[spec.weight]

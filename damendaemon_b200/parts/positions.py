@@ -9,8 +9,6 @@ from .spec import TensorDecl
 
 @register_position("learned")
 class LearnedPositions(PositionEncoding):
-    kernels_only = True
-
     def __init__(self, spec, weights, runtime):
         self.spec = spec
         self.table = weights[spec.table]
@@ -25,7 +23,5 @@ class LearnedPositions(PositionEncoding):
 
 @register_position("none")
 class NoPositions(PositionEncoding):
-    kernels_only = True
-
     def __init__(self, spec, weights, runtime):
         self.spec = spec
