@@ -12,7 +12,7 @@ import math
 import torch
 
 from ..config.gpt2 import ARCHITECTURE, Gpt2Config
-from ..parts.spec import (AttentionSpec, DenseFeedForwardSpec, LayerSpec, ModelSpec, NormSpec,
+from ..parts.spec import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, NormSpec,
                           PositionSpec, RunEntry)
 from ..registry import Architecture, register_architecture
 
@@ -26,13 +26,13 @@ def build_spec(c: Gpt2Config) -> ModelSpec:
             scale /= (i + 1)
         layers.append(LayerSpec(
             arrangement="pre_norm",
-            norm1=NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, p + "ln_1.weight", p + "ln_1.bias"),
+            norms=(NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, p + "ln_1.weight", p + "ln_1.bias"),
+                   NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, p + "ln_2.weight", p + "ln_2.bias")),
             mixer=AttentionSpec("attention", width=c.n_embd, n_heads=c.n_head, n_kv_heads=c.n_head,
                                 head_dim=c.head_dim, scale=scale, window=None,
                                 qkv_weight=p + "attn.c_attn.weight", qkv_bias=p + "attn.c_attn.bias",
                                 out_weight=p + "attn.c_proj.weight", out_bias=p + "attn.c_proj.bias",
                                 stored_in_out=True),
-            norm2=NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, p + "ln_2.weight", p + "ln_2.bias"),
             feed_forward=DenseFeedForwardSpec("dense", width=c.n_embd, inner=c.n_inner,
                                               activation=c.activation_function,
                                               up_weight=p + "mlp.c_fc.weight", up_bias=p + "mlp.c_fc.bias",
@@ -41,11 +41,14 @@ def build_spec(c: Gpt2Config) -> ModelSpec:
         ))
     return ModelSpec(
         architecture=ARCHITECTURE, vocab_size=c.vocab_size, width=c.n_embd, max_positions=c.n_positions,
-        token_table="wte.weight",
+        embedding=EmbeddingSpec("tokens", c.vocab_size, c.n_embd, table="wte.weight"),
         position=PositionSpec("learned", c.n_positions, c.n_embd, table="wpe.weight"),
         layers=tuple(layers), run_order=tuple(RunEntry(i) for i in range(c.n_layer)),
-        final_norm=NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, "ln_f.weight", "ln_f.bias"),
-        head_weight=None, eos_token_ids=tuple(c.eos_token_ids),
+        # the LM head is the token table (damendaemon/gpt2.py:18)
+        head=HeadSpec("linear", c.vocab_size, c.n_embd,
+                      norm=NormSpec("layernorm", c.n_embd, c.layer_norm_epsilon, "ln_f.weight", "ln_f.bias"),
+                      weight="wte.weight", tied=True),
+        eos_token_ids=tuple(c.eos_token_ids),
         # saved causal-mask buffers are not parameters (damendaemon/gpt2.py:26-28)
         ignored_tensors=(r"h\.\d+\.attn\.bias", r"h\.\d+\.attn\.masked_bias"),
         tied_duplicates=(("lm_head.weight", "wte.weight"),),

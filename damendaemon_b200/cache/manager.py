@@ -1,9 +1,11 @@
 """The cache manager: paged keys/values per layer group, block tables, per-request state slots.
 
-Layers declare what they need (``PagedKeyValues`` and/or ``RequestState``). Layers whose
-paged need is the same (heads, head size, window) form a *group*: one page pool, one
-block table per request, one arena ``[layers, pages, 2, kv_heads, page_size, head_dim]``
-in which a page index means the same page in every layer of the group. Groups with
+Layers declare what they need: a paged need (``PagedKeyValues``, or any other ``PagedNeed``
+that says what a page of it looks like) and/or a ``RequestState``. Layers whose paged need
+is the same (for keys and values: heads, head size, window) form a *group*: one page pool,
+one block table per request, one arena ``[layers, pages, *page shape]`` (for keys and values
+``[layers, pages, 2, kv_heads, page_size, head_dim]``) in which a page index means the same
+page in every layer of the group. Groups with
 different needs (all keys; a window of them) have pages of their own. Pages are given
 back when a request ends or, in a window group, once the window has passed them, and
 are handed out again (last freed, first reused).
@@ -28,11 +30,32 @@ import numpy as np
 from .pages import PageCapacityError, PagePool
 
 
+class PagedNeed:
+    """Per-token storage that grows with the request, kept in pages. A mixer may define its own (a frozen dataclass
+    that derives from this, so that equal needs compare equal and share a group): it gives ``window`` (None: every
+    earlier token stays; n: the last n), the shape of one page and a short label. The manager needs no more."""
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        raise NotImplementedError
+
+    @property
+    def label(self) -> str:
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
-class PagedKeyValues:
+class PagedKeyValues(PagedNeed):
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every earlier key stays; n: the last n keys
+
+    def page_shape(self, page_size):
+        return (2, self.kv_heads, page_size, self.head_dim)      # key plane and value plane, head-major inside a page
+
+    @property
+    def label(self):
+        return f"kv{self.kv_heads}x{self.head_dim}"
 
 
 @dataclass(frozen=True)
@@ -42,18 +65,19 @@ class RequestState:
 
 
 class CacheGroup:
-    def __init__(self, need: PagedKeyValues, layers, n_pages, page_size, max_requests, max_blocks):
+    def __init__(self, need: PagedNeed, layers, n_pages, page_size, max_requests, max_blocks):
         self.need, self.layers = need, list(layers)
         self.pool = PagePool(n_pages, page_size)
+        self.page_shape = tuple(int(n) for n in need.page_shape(page_size))
         self.tables = {}        # request id -> list of page ids, -1 where a page was given back
-        self.arena = None       # device tensor [len(layers), n_pages, 2, kv_heads, page_size, head_dim]
+        self.arena = None       # device tensor [len(layers), n_pages, *page_shape]
         # the same block tables by slot, ready to be copied to the device: -1 = no page
         self.table_array = np.full((max_requests, max_blocks), -1, dtype=np.int32)
 
     @property
     def name(self):
         w = "all" if self.need.window is None else f"w{self.need.window}"
-        return f"kv{self.need.kv_heads}x{self.need.head_dim}.{w}"
+        return f"{self.need.label}.{w}"
 
     def first_needed_block(self, length: int) -> int:
         """Blocks before this one hold only keys that no later query can see."""
@@ -90,7 +114,7 @@ class CacheManager:
         self.state_needs = {}                     # layer -> RequestState
         for layer, needs in enumerate(layer_needs):
             for need in needs or ():
-                if isinstance(need, PagedKeyValues):
+                if isinstance(need, PagedNeed):
                     by_need.setdefault(need, []).append(layer)
                 elif isinstance(need, RequestState):
                     self.state_needs[layer] = need
@@ -111,7 +135,7 @@ class CacheManager:
         import math
         total = 0
         for g in self.groups:
-            total += len(g.layers) * g.pool.n_pages * 2 * g.need.kv_heads * self.page_size * g.need.head_dim * element_size
+            total += len(g.layers) * g.pool.n_pages * math.prod(g.page_shape) * element_size
         widths = {"float32": 4, "bfloat16": 2, "float16": 2, "int32": 4, "int64": 8, "float64": 8}
         for need in self.state_needs.values():
             total += self.max_requests * math.prod(need.shape) * widths.get(need.dtype, 4)
@@ -120,9 +144,7 @@ class CacheManager:
     def allocate(self, device, dtype):
         import torch
         for g in self.groups:
-            n = g.need
-            g.arena = torch.zeros((len(g.layers), g.pool.n_pages, 2, n.kv_heads, self.page_size, n.head_dim),
-                                  device=device, dtype=dtype)
+            g.arena = torch.zeros((len(g.layers), g.pool.n_pages, *g.page_shape), device=device, dtype=dtype)
         for layer, need in self.state_needs.items():
             self.state[layer] = torch.zeros((self.max_requests, *need.shape), device=device,
                                             dtype=getattr(torch, need.dtype))
@@ -135,7 +157,8 @@ class CacheManager:
                           state=self.state.get(layer), page_size=self.page_size, writable=writable)
 
     def bytes_per_token(self, element_size):
-        return sum(len(g.layers) * 2 * g.need.kv_heads * g.need.head_dim * element_size for g in self.groups)
+        import math
+        return sum(len(g.layers) * math.prod(g.page_shape) // self.page_size * element_size for g in self.groups)
 
     # ---- requests ----
     def admit(self, request) -> int:
@@ -258,7 +281,11 @@ class CacheManager:
 @dataclass
 class LayerCache:
     group: Optional[CacheGroup]
-    kv: object
+    kv: object                 # this layer's pages [n_pages, *page shape] (keys and values: [n_pages, 2, kv_heads, page, head_dim])
     state: object
     page_size: int
     writable: bool = True      # False: this mixer reads another stop's cache and must not write it
+
+    @property
+    def pages(self):
+        return self.kv

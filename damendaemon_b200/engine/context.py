@@ -5,7 +5,6 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from .. import kernels
 
 
 @dataclass
@@ -24,7 +23,8 @@ class StepContext:
     host: dict = field(default_factory=dict)   # the same lists on the host, for parts that plan there
     decode_only: bool = False
     split_context: int = 0     # context length the key splits are planned for
-    aligned_starts: bool = False   # every entry starts at a multiple of the prompt attention's key block
+    aligned_starts: bool = False   # every entry starts at a multiple of the model's portion multiple (the key block of
+                                   # its prompt attention kernel), so no key block mixes cached and new keys
     runtime: object = None
     sm_count: int = 148
 
@@ -41,36 +41,7 @@ class StepContext:
     def attend(self, q, k, v, cache, n_heads, scale, window=None):
         """Put this step's keys and values into the layer's cache pages (unless the cache is another
         stop's, ``cache.writable == False``) and run paged causal attention of the step's tokens.
-        q, k, v: row views [N, heads * head_dim] of one buffer (the fused projection's output)."""
-        kv, table = cache.kv, self.block_table(cache.group)
-        kv_heads, head_dim = kv.shape[2], kv.shape[4]
-        fast = self.runtime.attention != "rows"
-        if self.decode_only and fast and self.runtime.attention != "mma" and self.n_tokens * n_heads >= 150 and \
-                kernels.attention_decode_pages_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype):
-            # whole pages of a group of heads by TMA; it too takes the new keys and values from the projection. Measured
-            # with 25 heads and 768 keys: faster than the row kernel from 8 tokens on (11.6 against 14.0 us; 54 against 68
-            # at 64), slower at 4 and below (11.0 against 9.8 us; 9.1 against 5.5 at one token), hence the threshold
-            splits = kernels.attention_decode_pages_splits(self.n_tokens, n_heads, kv.shape[3], self.split_context, q.device)
-            splits = max(splits, -(-table.shape[1] // 128))          # a block holds the ids of at most 128 pages
-            return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
-                                            n_splits=splits, k_new=k if cache.writable else None,
-                                            v_new=v if cache.writable else None, kernel="pages")
-        if self.decode_only and fast and kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
-            # the decode kernel takes the new keys and values from the projection and writes them itself
-            return kernels.attention_decode(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
-                                            n_splits=self.key_splits(n_heads, keys_per_block=128, blocks_per_sm=2),
-                                            k_new=k if cache.writable else None, v_new=v if cache.writable else None)
-        tcgen05 = not self.decode_only and fast and self.runtime.attention != "mma" and \
-            kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, kv.shape[3], q.dtype)
-        # the tcgen05 prompt kernel writes the cache itself when no key block mixes cached and new keys
-        fused_store = tcgen05 and cache.writable and self.aligned_starts
-        if cache.writable and not fused_store:
-            kernels.kv_store(k, v, self.token_entry, self.positions, table, kv)
-        if tcgen05:
-            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window,
-                                             kernel="tcgen05", k_new=k if cache.writable else None,
-                                             v_new=v if cache.writable else None, store_new=fused_store)
-        if not self.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype):
-            return kernels.attention_prefill(q, kv, self.entry_start, self.entry_pos0, table, n_heads, scale, window)
-        return kernels.attention_rows(q, kv, self.token_entry, self.positions, table, n_heads, scale, window,
-                                      n_splits=self.key_splits(n_heads))
+        q, k, v: row views [N, heads * head_dim] of one buffer (the fused projection's output).
+        Which kernel runs is decided in parts/paged_attention.py from the sizes and the runtime's tuning."""
+        from ..parts.paged_attention import paged_attention
+        return paged_attention(self, q, k, v, cache, n_heads, scale, window)

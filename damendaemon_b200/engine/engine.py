@@ -69,7 +69,7 @@ class Engine:
             weights = load_weights(model_dir, self.spec, decls, self.dtype, self.device)
         else:
             weights = check_and_place(DictSource(tensors), self.spec, decls, self.dtype, self.device)
-        self.runtime = Runtime(dtype=self.dtype, device=self.device, gemm=gemm)
+        self.runtime = Runtime(dtype=self.dtype, device=self.device, gemm=gemm, page_size=page_size)
         kernels.library("core")
         if self.dtype == torch.bfloat16 and gemm != "simt":
             kernels.library("tensor")
@@ -77,8 +77,9 @@ class Engine:
         self.weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
         self.page_size = page_size
         self.max_context = self.spec.max_positions
-        # where a scheduler should cut a prompt that it has to cut: at a key block of the bfloat16 prompt attention
-        self.portion_multiple = kernels.ATTENTION_PREFILL_TCGEN05_KEY_BLOCK if self.dtype == torch.bfloat16 else 1
+        # where a scheduler should cut a prompt that it has to cut: where the model's mixers like it (a key block of a
+        # prompt attention kernel), 1 if they do not care
+        self.portion_multiple = self.model.portion_multiple
         if kv_tokens is None:
             kv_tokens = max_requests * self.max_context
         kv_tokens = (kv_tokens + page_size - 1) // page_size * page_size
@@ -279,8 +280,8 @@ class Engine:
             a, b = at["ids"]
             self._meta_dev[a:b].copy_(device_ids.reshape(-1), non_blocking=True)
         host = {"lengths": lengths, "pos0": pos0, "slots": slots}
-        block = kernels.ATTENTION_PREFILL_TCGEN05_KEY_BLOCK
-        aligned = not decode_only and all(p % block == 0 for p in pos0)
+        block = self.portion_multiple
+        aligned = not decode_only and block > 1 and all(p % block == 0 for p in pos0)
         if self.use_graph and M > 0 and N <= self.max_graph_tokens:
             # Every kernel reads lengths, positions and page tables from the metadata buffer, and launch shapes
             # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.

@@ -1,6 +1,6 @@
-"""Block arrangements: how a layer's norm, mixer and feed-forward are wired.
+"""Block arrangements: how a layer's norms, mixer and feed-forward are wired.
 
-'pre_norm': x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))  (damendaemon/gpt2.py:47-64).
+'pre_norm': x = x + mixer(norm[0](x)); x = x + feed_forward(norm[1](x))  (damendaemon/gpt2.py:47-64).
 """
 from __future__ import annotations
 
@@ -9,9 +9,11 @@ from .registry import register_arrangement
 
 @register_arrangement("pre_norm")
 class PreNormBlock:
-    def __init__(self, spec, norm1, mixer, norm2, feed_forward):
-        self.spec, self.norm1, self.mixer, self.norm2, self.feed_forward = spec, norm1, mixer, norm2, feed_forward
+    def __init__(self, spec, norms, mixer, feed_forward):
+        if len(norms) != 2:
+            raise ValueError(f"a pre-norm block takes two norms (before the mixer, before the feed-forward), got {len(norms)}")
+        self.spec, self.norms, self.mixer, self.feed_forward = spec, list(norms), mixer, feed_forward
 
     def forward(self, x, ctx, cache, position):
-        x = self.mixer.forward(self.norm1.forward(x), x, ctx, cache, position)
-        return self.feed_forward.forward(self.norm2.forward(x), x, ctx)
+        x = self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, position)
+        return self.feed_forward.forward(self.norms[1].forward(x), x, ctx)

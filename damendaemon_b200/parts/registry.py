@@ -1,6 +1,6 @@
 """Registries from a part spec's ``kind`` to the class that implements it.
 
-Adding a mixer, feed-forward, norm, position encoding or block arrangement is one
+Adding a mixer, feed-forward, norm, position encoding, block arrangement, embedding or head is one
 ``register_*`` call with a class that has the interface in ``parts/interfaces.py``;
 nothing else in the framework changes.
 """
@@ -11,6 +11,8 @@ FEED_FORWARDS: dict = {}
 NORMS: dict = {}
 POSITIONS: dict = {}
 ARRANGEMENTS: dict = {}
+EMBEDDINGS: dict = {}
+HEADS: dict = {}
 
 
 def _register(table, what):
@@ -29,6 +31,8 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position = _register(POSITIONS, "position encoding")
 register_arrangement = _register(ARRANGEMENTS, "block arrangement")
+register_embedding = _register(EMBEDDINGS, "embedding")
+register_head = _register(HEADS, "head")
 
 
 def lookup(table, spec, what):

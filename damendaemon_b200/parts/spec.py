@@ -21,11 +21,17 @@ class TensorDecl:
     'vector' is always float32 (biases, norm parameters), 'int' is int32.
     ``stored_in_out``: the checkpoint holds the matrix as [in, out] (GPT-2 Conv1D);
     the device copy is always [out, in], K-contiguous.
+    ``pieces``: the checkpoint does not hold this tensor whole but as several tensors
+    ((checkpoint name, shape as stored), ...) that are joined along the output axis, in
+    this order, when they are placed (separate query, key and value projections that one
+    fused product reads); ``name`` is then only the key under which the part finds the
+    joined tensor, and ``shape`` its shape as if it had been stored whole.
     """
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
     stored_in_out: bool = False
+    pieces: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -54,8 +60,8 @@ class AttentionSpec:
     head_dim: int
     scale: float         # multiplies q.k (already includes any per-layer factor)
     window: Optional[int]  # None = all earlier keys; n = the query and the n-1 keys before it
-    qkv_weight: str
-    qkv_bias: Optional[str]
+    qkv_weight: object   # checkpoint name of the fused projection, or the three names (query, key, value) of separate ones
+    qkv_bias: object     # None, one name, or three names
     out_weight: str
     out_bias: Optional[str]
     stored_in_out: bool = False
@@ -76,15 +82,35 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    arrangement: str     # 'pre_norm'
+    """A layer: a mixer, a feed-forward, as many norms as its arrangement wants, and the arrangement that wires them
+    ('pre_norm' takes two norms: before the mixer, before the feed-forward)."""
+    arrangement: str
     mixer: object
     feed_forward: object
-    norm1: object
-    norm2: object
+    norms: Tuple[object, ...]
 
     @property
     def kind(self):
         return self.arrangement
+
+
+@dataclass(frozen=True)
+class EmbeddingSpec:
+    kind: str            # 'tokens': a row of the table per token id (the position encoding may add its own table)
+    vocab_size: int
+    width: int
+    table: str           # checkpoint name
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    kind: str            # 'linear': final norm on the wanted rows, then logits = y . W^T (+ bias)
+    vocab_size: int
+    width: int
+    norm: object         # a norm spec
+    weight: str          # checkpoint name of W [vocab, width]
+    tied: bool = False   # W is the embedding's table (declared there, not again)
+    bias: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -106,13 +132,17 @@ class ModelSpec:
     vocab_size: int
     width: int
     max_positions: int
-    token_table: str                  # checkpoint name of the token embedding
+    embedding: object                 # an embedding spec
     position: object                  # a position-encoding spec
     layers: Tuple[LayerSpec, ...]
     run_order: Tuple[RunEntry, ...]
-    final_norm: object
-    head_weight: Optional[str] = None  # None: the LM head is the token table (tied)
+    head: object                      # a head spec (with the final norm)
     eos_token_ids: Tuple[int, ...] = ()
     ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)   # regexes of tensors to drop
     tied_duplicates: Tuple[Tuple[str, str], ...] = field(default_factory=tuple)  # (name, must equal)
     optional_prefix: str = ""          # e.g. 'transformer.': stripped from every name when present
+
+    @property
+    def prefix_probe(self):
+        """The tensor whose presence under the optional prefix says that the checkpoint uses the prefix."""
+        return self.embedding.table

@@ -22,6 +22,7 @@ from pathlib import Path
 
 import torch
 
+from ..parts.spec import TensorDecl
 from .safetensors_io import SafetensorsFile
 
 _FLOATING = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
@@ -89,10 +90,17 @@ def check_and_place(source, spec, decls, engine_dtype, device):
     names = list(source.names())
     prefix = spec.optional_prefix
     strip = bool(prefix) and any(n.startswith(prefix) for n in names) and \
-        (prefix + spec.token_table) in names
+        (prefix + spec.prefix_probe) in names
     rename = {(n[len(prefix):] if strip and n.startswith(prefix) else n): n for n in names}
     ignored = [re.compile(p) for p in spec.ignored_tensors]
-    wanted = {d.name: d for d in decls}
+    # what the checkpoint must hold: every declared tensor, or its pieces where it is stored in pieces
+    wanted = {}
+    for d in decls:
+        if d.pieces:
+            for piece_name, piece_shape in d.pieces:
+                wanted[piece_name] = TensorDecl(piece_name, tuple(piece_shape), d.role, d.stored_in_out)
+        else:
+            wanted[d.name] = d
     duplicates = dict(spec.tied_duplicates)
 
     missing = [n for n in wanted if n not in rename]
@@ -131,10 +139,17 @@ def check_and_place(source, spec, decls, engine_dtype, device):
 
     placed = {}
     for decl in decls:
-        t = source.tensor(rename[decl.name])
-        if decl.role in ("matrix", "table"):
-            if decl.stored_in_out:
+        if decl.pieces:
+            # joined along the output axis: rows of the [out, in] device copy, the only axis of a vector
+            parts = [source.tensor(rename[n]) for n, _ in decl.pieces]
+            t = torch.cat([p.t() if decl.stored_in_out and p.dim() == 2 else p for p in parts], dim=0)
+            if tuple(t.shape) != (tuple(reversed(decl.shape)) if decl.stored_in_out and len(decl.shape) == 2 else tuple(decl.shape)):
+                raise ValueError(f"the pieces of {decl.name} do not add up to {tuple(decl.shape)}")
+        else:
+            t = source.tensor(rename[decl.name])
+            if decl.role in ("matrix", "table") and decl.stored_in_out:
                 t = t.t()
+        if decl.role in ("matrix", "table"):
             t = t.to(device=device, dtype=engine_dtype).contiguous()
         elif decl.role == "vector":
             t = t.to(device=device, dtype=torch.float32).contiguous()

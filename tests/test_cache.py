@@ -159,3 +159,43 @@ def test_random_orders(seed, window):
         m.release(r)
     m.check()
     assert m.used_tokens == 0
+
+
+def test_a_paged_need_of_a_mixers_own():
+    """A need the manager has never heard of (one plane of compressed rows instead of keys and values): a frozen
+    dataclass that says what a page looks like. It gets a group, an arena and block tables of its own, beside the
+    keys and values of other layers, with no change to the manager."""
+    import torch
+    from dataclasses import dataclass
+    from typing import Optional
+    from damendaemon_b200.cache import PagedNeed
+
+    @dataclass(frozen=True)
+    class LatentRows(PagedNeed):
+        width: int
+        window: Optional[int] = None
+
+        def page_shape(self, page_size):
+            return (page_size, self.width)
+
+        @property
+        def label(self):
+            return f"latent{self.width}"
+
+    m = CacheManager([[PagedKeyValues(2, 16)], [LatentRows(24)], [LatentRows(24)], [LatentRows(24, window=20)]], 128, 8, 3, 64)
+    assert [g.name for g in m.groups] == ["kv2x16.all", "latent24.all", "latent24.w20"]
+    assert [g.layers for g in m.groups] == [[0], [1, 2], [3]]
+    assert m.bytes_needed(2) == 16 * (1 * 2 * 2 * 8 * 16 + 2 * 8 * 24 + 1 * 8 * 24) * 2
+    assert m.bytes_per_token(2) == (2 * 2 * 16 + 2 * 24 + 24) * 2
+    m.allocate("cpu", torch.float32)
+    assert m.groups[1].arena.shape == (2, 16, 8, 24) and m.layer_view(2).pages.shape == (16, 8, 24)
+    assert m.layer_view(0).kv.shape == (16, 2, 2, 8, 16)
+    m.admit("a")
+    m.extend([("a", 30)])
+    m.advance("a", 30)
+    assert m.groups[1].tables["a"] == [0, 1, 2, 3] and m.groups[2].tables["a"] == [-1, 1, 2, 3]
+    m.release("a")
+    m.check()
+    assert m.used_tokens == 0
+    with pytest.raises(TypeError):
+        CacheManager([[object()]], 128, 8, 3, 64)

@@ -73,4 +73,4 @@ def test_spec_has_no_hidden_sizes(tiny_configs):
     assert (m.n_heads, m.n_kv_heads, m.head_dim, m.window) == (2, 2, 48, None)
     assert m.scale == pytest.approx(48 ** -0.5 / 3)
     assert spec.layers[0].feed_forward.inner == 320 and spec.layers[0].feed_forward.activation == "gelu"
-    assert spec.final_norm.eps == 1e-6 and spec.position.n_positions == 256
+    assert spec.head.norm.eps == 1e-6 and spec.position.n_positions == 256

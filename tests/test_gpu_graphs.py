@@ -79,7 +79,8 @@ def test_replayed_prompt_and_mixed_steps(model_c, dtype):
     # (5 times), the second portions off a key-block boundary (4 times; the trial whose second portions start at 128 has
     # the same counts but starts on boundaries, another shape, seen once), the mixed step (5), the decode step (15).
     assert len(engine._graphs) == 4
-    assert engine.graph_replays == 4 + 3 + 4 + 14
+    # (a float32 engine's attention has no key blocks: there the odd trial's second portions are the same shape as the others')
+    assert engine.graph_replays == (4 + 3 + 4 + 14 if engine.portion_multiple > 1 else 4 + 4 + 4 + 14)
     assert engine.raise_device_errors() is None and checked == len(trials) * 22
 
 

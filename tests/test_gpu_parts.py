@@ -9,7 +9,7 @@ import torch
 
 import plain_gpt2 as plain
 from damendaemon_b200.cache import CacheManager, RequestState
-from damendaemon_b200.parts import (AttentionSpec, DenseFeedForwardSpec, LayerSpec, ModelSpec, NormSpec, PositionSpec,
+from damendaemon_b200.parts import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, NormSpec, PositionSpec,
                                     RunEntry, Runtime, TensorDecl, register_mixer)
 from damendaemon_b200.parts.interfaces import Mixer
 from damendaemon_b200.registry import Architecture, register_architecture
@@ -171,14 +171,15 @@ def toy_spec(c):
     ff = lambda i: DenseFeedForwardSpec("dense", c.width, 2 * c.width, "gelu_new", f"l{i}.up.weight", f"l{i}.up.bias",
                                         f"l{i}.down.weight", f"l{i}.down.bias")
     layers = (
-        LayerSpec("pre_norm", ToyStateSpec("toy_state", c.width, "l0.gain"), ff(0), norm("l0.n1"), norm("l0.n2")),
+        LayerSpec("pre_norm", ToyStateSpec("toy_state", c.width, "l0.gain"), ff(0), (norm("l0.n1"), norm("l0.n2"))),
         LayerSpec("pre_norm", AttentionSpec("attention", c.width, 2, 1, c.width // 2, (c.width // 2) ** -0.5, None,
-                                            "l1.qkv.weight", None, "l1.out.weight", None), ff(1), norm("l1.n1"), norm("l1.n2")),
+                                            "l1.qkv.weight", None, "l1.out.weight", None), ff(1), (norm("l1.n1"), norm("l1.n2"))),
     )
     # layer 1 runs twice: the order of layers is data. "twice": each run has its own cache;
     # "borrow": the second run reads the keys and values of the first and writes none
-    return ModelSpec("ToyStateLM", c.vocab, c.width, c.positions, "embed.weight", PositionSpec("learned", c.positions, c.width, "pos.weight"),
-                     layers, RUN_ORDERS[c.order], norm("final"))
+    return ModelSpec("ToyStateLM", c.vocab, c.width, c.positions, EmbeddingSpec("tokens", c.vocab, c.width, "embed.weight"),
+                     PositionSpec("learned", c.positions, c.width, "pos.weight"), layers, RUN_ORDERS[c.order],
+                     HeadSpec("linear", c.vocab, c.width, norm("final"), "embed.weight", tied=True))
 
 
 def toy_tensors(c, seed, dtype=torch.float32):

@@ -124,3 +124,44 @@ def test_sharded_checkpoint(tmp_path):
     (tmp_path / "model-00002-of-00002.safetensors").unlink()
     with pytest.raises(WeightError, match="shards"):
         load_weights(tmp_path, spec, decls, torch.float32, "cpu")
+
+
+def test_tensors_stored_in_pieces_are_joined_at_load(tmp_path):
+    """Separate query, key and value projections in the checkpoint (stored [in, out] here, and with grouped key/value
+    heads so that the three differ in width) become the one fused matrix the attention mixer reads; a missing or
+    misshapen piece is named in the one error."""
+    import torch
+    from damendaemon_b200.parts import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec,
+                                        NormSpec, PositionSpec, RunEntry, tensor_decls)
+    from damendaemon_b200.weights import DictSource, WeightError, check_and_place
+    width, heads, kv_heads, d = 32, 4, 2, 8
+    norm = lambda n: NormSpec("layernorm", width, 1e-5, n + ".weight", n + ".bias")
+    mixer = AttentionSpec("attention", width, heads, kv_heads, d, d ** -0.5, None,
+                          qkv_weight=("q.weight", "k.weight", "v.weight"), qkv_bias=("q.bias", "k.bias", "v.bias"),
+                          out_weight="o.weight", out_bias=None, stored_in_out=True)
+    ff = DenseFeedForwardSpec("dense", width, 64, "gelu_new", "up.weight", None, "down.weight", None)
+    spec = ModelSpec("Pieces", 50, width, 16, EmbeddingSpec("tokens", 50, width, "embed.weight"), PositionSpec("none", 16, width),
+                     (LayerSpec("pre_norm", mixer, ff, (norm("n1"), norm("n2"))),), (RunEntry(0),),
+                     HeadSpec("linear", 50, width, norm("nf"), "head.weight"))
+    decls = tensor_decls(spec)
+    joined = next(d_ for d_ in decls if d_.name == "q.weight+k.weight+v.weight")
+    assert joined.shape == (width, 64) and [n for n, _ in joined.pieces] == ["q.weight", "k.weight", "v.weight"]
+    g = torch.Generator().manual_seed(0)
+    tensors = {}
+    for d_ in decls:
+        for name, shape in (d_.pieces or ((d_.name, d_.shape),)):
+            tensors[name] = torch.randn(shape, generator=g)
+    placed = check_and_place(DictSource(tensors), spec, decls, torch.float32, "cpu")
+    fused = placed["q.weight+k.weight+v.weight"]
+    assert fused.shape == (64, width) and fused.is_contiguous()
+    assert torch.equal(fused, torch.cat([tensors["q.weight"].t(), tensors["k.weight"].t(), tensors["v.weight"].t()]))
+    assert torch.equal(placed["q.bias+k.bias+v.bias"], torch.cat([tensors["q.bias"], tensors["k.bias"], tensors["v.bias"]]))
+    assert "head.weight" in placed and placed["head.weight"].shape == (50, width)       # an untied head has its own matrix
+    broken = dict(tensors)
+    del broken["k.weight"]
+    broken["v.bias"] = torch.zeros(9)
+    broken["q.weight+k.weight+v.weight"] = torch.zeros(width, 64)
+    with pytest.raises(WeightError) as info:
+        check_and_place(DictSource(broken), spec, decls, torch.float32, "cpu")
+    assert info.value.missing == ["k.weight"] and info.value.unexpected == ["q.weight+k.weight+v.weight"]
+    assert any(w.startswith("v.bias") for w in info.value.wrong_shape)
