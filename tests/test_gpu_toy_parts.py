@@ -204,7 +204,10 @@ def test_toy_architecture_of_outside_parts(dtype):
         want[r] = toy_plain(c, tensors, ids).float()
         margin = min(margin, toy_plain.closest_call)
     assert margin > 0.02, "the router sits on a fence for some token; rounding would decide: choose other seeds"
-    tol = 1e-4 if dtype == "float32" else 8e-2
+    # float32: the engine's 1e-4 stands for GPT-2's logits of a few units; this model's weights are ten times larger and
+    # its logits reach beyond 8, so the bound is the same relative one, 3e-5 of the largest logit
+    peak = max(float(v.abs().max()) for v in want.values())
+    tol = 3e-5 * peak if dtype == "float32" else 2.0 ** -7 * peak
     got_a = [engine.step([StepEntry("a", a[:9], list(range(9)))])]
     both = engine.step([StepEntry("a", a[9:40], list(range(31))), StepEntry("b", b[:17], list(range(17)))])
     got_a.append(both[:31]); got_b = [both[31:]]
