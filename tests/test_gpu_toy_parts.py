@@ -136,19 +136,24 @@ def toy_tensors(c, seed, dtype=torch.float32, device="cpu"):
     out = {}
     for decl in tensor_decls(toy_spec(c)):
         for name, shape in (decl.pieces or ((decl.name, decl.shape),)):
-            t = torch.randn(shape, generator=g) * (0.25 if len(shape) == 2 else 0.1)
+            t = torch.randn(shape, generator=g) * (0.12 if len(shape) == 2 else 0.1)
             if name.endswith((".n1.weight", ".n2.weight", ".n.weight", "final.weight")):
                 t = t + 1
-            if name.endswith((".q.weight", ".k.weight", "router.weight")):
-                t = t * 3            # peaky attention and a router that decides
+            if name.endswith("router.weight"):
+                t = t * 6            # a router that decides
+            if name.endswith((".q.weight", ".k.weight")):
+                t = t * 1.5          # attention that is not nearly uniform, yet whose scores bfloat16 can still carry
             out[name] = t.to(dtype) if len(shape) == 2 else t
     return out
 
 
-def toy_plain(c, w, ids):
+def toy_plain(c, w, ids, rounded=None):
+    """rounded: a dtype to which the activations that a reduced-precision engine stores between kernels are rounded
+    (as plain_gpt2.logits_of does): what that rounding alone does to this model's logits is what a tolerance must allow."""
+    keep = (lambda t: t) if rounded is None else (lambda t: t.to(rounded).to(t.dtype))
     w = {k: v.double() for k, v in w.items()}
     T, d = len(ids), c.width // c.heads
-    ln = lambda x, n: plain.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5)
+    ln = lambda x, n: keep(plain.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5))
 
     def rotate(x):           # [T, heads, d]
         freq = 100.0 ** (-torch.arange(0, d // 2, dtype=torch.float64) * 2 / d)
@@ -158,11 +163,11 @@ def toy_plain(c, w, ids):
         return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
 
     def attend(y, i, window):
-        q = rotate((y @ w[f"l{i}.q.weight"].t()).reshape(T, c.heads, d))
-        k = rotate((y @ w[f"l{i}.k.weight"].t()).reshape(T, c.kv_heads, d))
-        v = (y @ w[f"l{i}.v.weight"].t()).reshape(T, c.kv_heads, d)
+        q = keep(rotate(keep(y @ w[f"l{i}.q.weight"].t()).reshape(T, c.heads, d)))
+        k = keep(rotate(keep(y @ w[f"l{i}.k.weight"].t()).reshape(T, c.kv_heads, d)))
+        v = keep(y @ w[f"l{i}.v.weight"].t()).reshape(T, c.kv_heads, d)
         share = c.heads // c.kv_heads
-        o = plain.causal_attention(q, k.repeat_interleave(share, 1), v.repeat_interleave(share, 1), d ** -0.5, window)
+        o = keep(plain.causal_attention(q, k.repeat_interleave(share, 1), v.repeat_interleave(share, 1), d ** -0.5, window))
         return o.reshape(T, c.width) @ w[f"l{i}.o.weight"].t()
 
     x = w["embed.weight"][torch.as_tensor(ids)]
@@ -174,11 +179,11 @@ def toy_plain(c, w, ids):
     toy_plain.closest_call = float((top2[:, 0] - top2[:, 1]).min())      # how near the router came to a tie
     moe = torch.zeros_like(x)
     for e in range(c.experts):
-        hidden = plain.gelu_new(y @ w[f"l0.moe.e{e}.up.weight"].t() + w[f"l0.moe.e{e}.up.bias"])
+        hidden = keep(plain.gelu_new(y @ w[f"l0.moe.e{e}.up.weight"].t() + w[f"l0.moe.e{e}.up.bias"]))
         moe += (choice == e)[:, None] * gate[:, None] * (hidden @ w[f"l0.moe.e{e}.down.weight"].t())
     x = x + moe
     y = ln(x, "l1.n")
-    x = x + attend(y, 1, c.window) + plain.gelu_erf(y @ w["l1.up.weight"].t()) @ w["l1.down.weight"].t() + w["l1.down.bias"]
+    x = x + attend(y, 1, c.window) + keep(plain.gelu_erf(y @ w["l1.up.weight"].t())) @ w["l1.down.weight"].t() + w["l1.down.bias"]
     return ln(x, "final") @ w["head.weight"].t() + w["head.bias"]
 
 
@@ -191,7 +196,7 @@ def test_toy_architecture_of_outside_parts(dtype):
     register_architecture(Architecture("ToyMixLM", lambda raw: ToyMixConfig(**{k: v for k, v in raw.items() if k != "architectures"}),
                                        toy_spec, lambda c, seed, dt=torch.float32, device="cpu": toy_tensors(c, seed, dt)), replace=True)
     c = ToyMixConfig()
-    tensors = toy_tensors(c, 7, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    tensors = toy_tensors(c, 17, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
     engine = Engine(config=c.to_dict(), tensors=tensors, dtype=dtype, kv_tokens=160, page_size=8, max_requests=3)
     # two cache groups: all keys for layer 0, a window of them for layer 1, each with pages of its own
     assert [g.name for g in engine.cache.groups] == ["kv2x16.all", "kv2x16.w11"]
@@ -199,15 +204,17 @@ def test_toy_architecture_of_outside_parts(dtype):
         group.arena.fill_(float("nan"))
     g = torch.Generator().manual_seed(6)
     a, b = (torch.randint(0, c.vocab, (n,), generator=g).tolist() for n in (70, 33))
-    want, margin = {}, 1.0
+    want, margin, moved = {}, 1.0, 0.0
     for r, ids in (("a", a), ("b", b)):
         want[r] = toy_plain(c, tensors, ids).float()
         margin = min(margin, toy_plain.closest_call)
+        moved = max(moved, float((toy_plain(c, tensors, ids, rounded=torch.bfloat16).float() - want[r]).abs().max()))
     assert margin > 0.02, "the router sits on a fence for some token; rounding would decide: choose other seeds"
     # float32: the engine's 1e-4 stands for GPT-2's logits of a few units; this model's weights are ten times larger and
-    # its logits reach beyond 8, so the bound is the same relative one, 3e-5 of the largest logit
+    # its logits reach beyond 8, so the bound is the same relative one, 3e-5 of the largest logit. bfloat16: three times
+    # what rounding the stored activations does to the plain logits of this very model, as in the engine's own tests.
     peak = max(float(v.abs().max()) for v in want.values())
-    tol = 3e-5 * peak if dtype == "float32" else 2.0 ** -7 * peak
+    tol = 3e-5 * peak if dtype == "float32" else 3.0 * moved + 2e-3
     got_a = [engine.step([StepEntry("a", a[:9], list(range(9)))])]
     both = engine.step([StepEntry("a", a[9:40], list(range(31))), StepEntry("b", b[:17], list(range(17)))])
     got_a.append(both[:31]); got_b = [both[31:]]
