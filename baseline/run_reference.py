@@ -95,7 +95,8 @@ def child(args):
         elapsed = max(done) - start
         value = tokens / elapsed if elapsed > 0 and tokens > 0 else None
         print(json.dumps({
-            "impl": "reference", "metric": f"decode tok/s at batch {batch} (GPT-2 XL shape, context 512->1024)",
+            "impl": "reference", "metric": f"decode tok/s at batch {batch} (GPT-2 XL shape, prompts of {prompt_len}, timed steps at context "
+                                           f"{prompt_len + 2}->{prompt_len + new_tokens})",
             "value": None if value is None else round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": None if value is None else round(1000.0 * batch / value, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",

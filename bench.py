@@ -83,7 +83,7 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_runtime(config, batch, use_graph=True, seed=0):
+def make_runtime(config, batch, use_graph=True, seed=0, dtype="bfloat16"):
     import torch
     from damendaemon_b200.registry import architecture_of
     from damendaemon_b200.runtime import Runtime
@@ -91,7 +91,7 @@ def make_runtime(config, batch, use_graph=True, seed=0):
     typed = arch.parse_config(config)
     tensors = arch.random_tensors(typed, seed, torch.bfloat16, device="cuda")
     slots = max(batch, 2)           # the prefill of two prompts runs on the same engine
-    runtime = Runtime(None, config=config, tensors=tensors, dtype="bfloat16", max_batch=slots,
+    runtime = Runtime(None, config=config, tensors=tensors, dtype=dtype, max_batch=slots,
                       kv_cache_tokens=slots * config["n_positions"], use_graph=use_graph, token_budget=4096)
     del tensors
     torch.cuda.empty_cache()
@@ -112,12 +112,12 @@ def prefill_all(engine, prompts, budget=4096):
         engine.step([StepEntry(r, prompts[r], []) for r in names[i:i + per]])
 
 
-def decode_device_timed(engine, batch, warmup, steps, vocab):
+def decode_device_timed(engine, batch, warmup, steps, vocab, prompt_len=PROMPT):
     """K decode steps with tokens known in advance, timed on the device. Returns (ms per step, bytes per step, launches per step)."""
     import torch
     from damendaemon_b200 import kernels
     from damendaemon_b200.engine import StepEntry
-    prompts = {f"d{i}": random_ids(PROMPT, vocab, 100 + i) for i in range(batch)}
+    prompts = {f"d{i}": random_ids(prompt_len, vocab, 100 + i) for i in range(batch)}
     prefill_all(engine, prompts)
     feed = [random_ids(batch, vocab, 1000 + s) for s in range(warmup + steps)]
 
@@ -139,7 +139,7 @@ def decode_device_timed(engine, batch, warmup, steps, vocab):
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps
     kv_per_token = engine.cache.bytes_per_token(2)
-    contexts = [PROMPT + s + 1 for s in range(warmup, warmup + steps)]
+    contexts = [prompt_len + s + 1 for s in range(warmup, warmup + steps)]
     position_table = engine.spec.max_positions * engine.spec.width * 2
     bytes_per_step = engine.weight_bytes - position_table + batch * kv_per_token * statistics.mean(contexts)
     for r in prompts:
@@ -211,7 +211,7 @@ WORKLOADS = {
 }
 
 
-def run_workload(name):
+def run_workload(name, dtype="bfloat16"):
     """The scheduler under a mixed load (continuous batching): total generated tokens per second and the step mix."""
     import random
     import torch
@@ -220,7 +220,7 @@ def run_workload(name):
     spec = WORKLOADS[name]
     config = spec["config"]
     vocab = config["vocab_size"]
-    runtime = make_runtime(config, spec["max_live"])
+    runtime = make_runtime(config, spec["max_live"], dtype=dtype)
     rng = random.Random(0)
     if name == "medium":
         scheduler = Scheduler(runtime.engine, token_budget=2048, chunk_size=512, max_live=32)
@@ -241,12 +241,61 @@ def run_workload(name):
     generated = sum(len(r.output) for r in requests)
     prompt_tokens = sum(len(r.prompt) for r in requests)
     mixed = sum(1 for p, d in scheduler.step_log if p and d)
+    run_workload.outputs = [list(r.output) for r in requests]
     return {"workload": name, "metric": "generated tokens/s through the scheduler", "value": round(generated / wall, 1),
             "unit": "tokens/s", "requests": len(requests), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
             "prompt_tokens_per_s": round(prompt_tokens / wall, 1), "seconds": round(wall, 3), "steps": scheduler.steps,
             "steps_mixing_prompt_and_decode": mixed, "failed": sum(1 for r in requests if r.finish_reason == "error"),
-            "config": {"n_layer": config["n_layer"], "n_embd": config["n_embd"], "n_head": config["n_head"], "dtype": "bf16",
+            "config": {"n_layer": config["n_layer"], "n_embd": config["n_embd"], "n_head": config["n_head"], "dtype": dtype,
                        "note": "first run of each step shape is eager and captures a CUDA graph; no warm-up pass"}}
+
+
+def parity(layers):
+    """The float32 engine beside the bfloat16 one on the benchmark's own model (seeded random weights): two requests,
+    a 512-token prompt and 32 teacher-forced decode steps each. Reports the largest difference of the float32
+    logits from the plain float64 implementation (tests/plain_gpt2.py, run on the GPU) and of the bfloat16 logits from
+    the float32 ones, and how often the greedy tokens agree."""
+    import torch
+    from damendaemon_b200.engine import Engine, StepEntry
+    from damendaemon_b200.registry import architecture_of
+    sys.path.insert(0, str(ROOT / "tests"))
+    import plain_gpt2
+    config = {**XL, "n_layer": layers}
+    arch = architecture_of(config)
+    tensors = arch.random_tensors(arch.parse_config(config), 0, torch.float32, device="cuda")
+    for name, t in tensors.items():
+        if t.dim() == 2:
+            tensors[name] = t.to(torch.bfloat16).float()        # both engines and the plain side read the same numbers
+    requests = {f"p{i}": random_ids(PROMPT + 32, config["vocab_size"], 40 + i) for i in range(2)}
+    rows = list(range(PROMPT - 1, PROMPT + 32))
+    w = {k: v.double() for k, v in tensors.items()}
+    want = {r: plain_gpt2.logits_of(config, w, ids, rows=rows).float() for r, ids in requests.items()}
+    del w
+    torch.cuda.empty_cache()
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine(config=config, tensors=tensors, dtype=dtype, kv_tokens=2 * 1024, page_size=16, max_requests=2,
+                        use_graph=True)
+        out = {r: [] for r in requests}
+        first = engine.step([StepEntry(r, ids[:PROMPT], [PROMPT - 1]) for r, ids in requests.items()])
+        for i, r in enumerate(requests):
+            out[r].append(first[i].clone())
+        for s in range(32):
+            logits = engine.step([StepEntry(r, [ids[PROMPT + s]], [0]) for r, ids in requests.items()])
+            for i, r in enumerate(requests):
+                out[r].append(logits[i].clone())
+        got[dtype] = {r: torch.stack(v) for r, v in out.items()}
+        del engine
+        torch.cuda.empty_cache()
+    worst = lambda a, b: max(float((a[r] - b[r]).abs().max()) for r in requests)
+    same = lambda a, b: sum(int((a[r].argmax(-1) == b[r].argmax(-1)).sum()) for r in requests)
+    total = 33 * len(requests)
+    return {"parity": "GPT-2 XL shape, seeded random weights, 2 requests x (512-token prompt + 32 forced decode steps)",
+            "n_layer_run": layers, "rows_compared": total,
+            "float32_vs_plain_float64": {"max_abs_logit_diff": worst(got["float32"], want), "same_greedy": same(got["float32"], want)},
+            "bfloat16_vs_float32": {"max_abs_logit_diff": worst(got["bfloat16"], got["float32"]),
+                                    "same_greedy": same(got["bfloat16"], got["float32"])},
+            "logit_scale": float(max(v.abs().max() for v in want.values()))}
 
 
 def reference_arm(args):
@@ -285,6 +334,8 @@ def main():
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
+    parser.add_argument("--parity", action="store_true", help="the float32 engine beside the bfloat16 one: on the benchmark's model "
+                        "(logit differences, greedy agreement), or with --workload on that workload (the same requests in both)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -292,7 +343,22 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     if args.workload:
-        print(json.dumps(run_workload(args.workload)), flush=True)
+        result = run_workload(args.workload)
+        if args.parity:
+            # the same requests through the float32 engine: greedy tokens agree until rounding flips a near tie
+            half = run_workload.outputs
+            result["float32"] = {k: v for k, v in run_workload(args.workload, dtype="float32").items()
+                                 if k in ("value", "seconds", "steps", "failed")}
+            full = run_workload.outputs
+            common = [next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), min(len(x), len(y))) for x, y in zip(half, full)]
+            result["parity"] = {"requests_with_the_same_first_token": sum(1 for n in common if n >= 1), "requests": len(common),
+                                "mean_common_prefix": round(sum(common) / len(common), 2),
+                                "note": "sampled at a temperature (medium): equal draws, so tokens agree until rounding moves one across a boundary"
+                                if args.workload == "medium" else "greedy: tokens agree until rounding flips a near tie"}
+        print(json.dumps(result), flush=True)
+        return 0
+    if args.parity:
+        print(json.dumps(parity(args.layers or XL["n_layer"])), flush=True)
         return 0
     if args.kernel_case:
         from bench_kernel_cases import time_case
@@ -327,18 +393,31 @@ def main():
             steps = min(args.steps, 128)
             point_ms, _, _ = decode_device_timed(rt.engine, batch, args.warmup, steps, vocab)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
+            if batch == 64:
+                # the cache-dominated end: 64 requests at context 1,000 -> 1,020
+                for r in list(rt.engine.live_requests()):
+                    rt.engine.finish(r)
+                long_ms, long_bytes, _ = decode_device_timed(rt.engine, batch, 3, 16, vocab, prompt_len=1000)
+                points["decode_b64_ctx1000"] = round(batch * 1000.0 / long_ms, 1)
+                points["decode_b64_ctx1000_hbm_frac"] = round(long_bytes / (long_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
             del rt
             torch.cuda.empty_cache()
+        if layers == XL["n_layer"]:
+            for name in sorted(WORKLOADS):          # the scheduler under mixed loads (generated tokens a second)
+                points[f"workload_{name}"] = run_workload(name)["value"]
+                torch.cuda.empty_cache()
 
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": f"decode tok/s at batch {args.batch} (GPT-2 XL shape, context 512->1024)",
+        "metric": f"decode tok/s at batch {args.batch} (GPT-2 XL shape, prompts of {PROMPT}, timed steps at context "
+                  f"{PROMPT + args.warmup + 1}->{PROMPT + args.warmup + args.steps})",
         "value": round(args.batch * 1000.0 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": "gpt2-xl-shape", "n_layer": XL["n_layer"], "n_layer_run": layers, "n_embd": 1600, "n_head": 25,
                    "head_dim": 64, "n_inner": 6400, "vocab_size": vocab, "n_positions": 1024, "global_batch": args.batch,
-                   "seq_len": 1024, "prompt_len": PROMPT, "page_size": 16, "kv_dtype": "bf16", "weights": "random bf16",
+                   "seq_len": 1024, "prompt_len": PROMPT, "page_size": 16, "weights": "random bf16, cache bf16",
+                   "context_timed": f"{PROMPT + args.warmup + 1}-{PROMPT + args.warmup + args.steps}",
                    "parallelism": "single-gpu", "l2": "inputs>L2 (3.1 GB of weights read per step)", "cuda_graph": not args.no_graph,
                    "activation": "gelu_new", "peaks": peak_source},
         "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 3),
