@@ -158,6 +158,9 @@ def read_error_flag(device):
     value = int(flag.item())
     if value:
         flag.zero_()
+        key = torch.device(device).index or 0
+        if value & 8 and key in _counters:
+            _counters[key].zero_()       # a kernel that gave up may have left a split counter short of its reset
     return value
 
 
