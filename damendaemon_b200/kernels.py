@@ -157,11 +157,17 @@ def read_error_flag(device):
     flag = error_flag(device)
     value = int(flag.item())
     if value:
-        flag.zero_()
-        key = torch.device(device).index or 0
-        if value & 8 and key in _counters:
-            _counters[key].zero_()       # a kernel that gave up may have left a split counter short of its reset
+        clear_after_error(device, value)
     return value
+
+
+def clear_after_error(device, bits):
+    """Zero the device's error word (in stream order) and, after a wait that ran out (bit 8), the split counters:
+    a kernel that gave up may have left one short of its reset."""
+    error_flag(device).zero_()
+    key = torch.device(device).index or 0
+    if bits & 8 and key in _counters:
+        _counters[key].zero_()
 
 
 def wait_probe(limit_ns, device):

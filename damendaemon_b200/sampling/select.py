@@ -79,7 +79,7 @@ def read_sampled(pending):
     *tokens, bits = pending.host.tolist()
     if bits:
         # in stream order this clears the word after every step launched so far, the one launched ahead included
-        kernels.error_flag(pending.ids.device).zero_()
+        kernels.clear_after_error(pending.ids.device, bits)
         raise DeviceStepError(f"a kernel reported error bits {bits:#x} (1 bad token/position, 2 bad page on write, "
                               "4 bad page on read, 8 wait timed out)")
     if any(t < 0 for t in tokens):

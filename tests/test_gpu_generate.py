@@ -179,3 +179,31 @@ def test_command_line(folders, tmp_path):
     made = subprocess.run([sys.executable, "-m", "damendaemon_b200", "init-random", str(cfg), str(tmp_path / "m"), "--seed", "4"],
                           capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert made.returncode == 0 and (tmp_path / "m" / "model.safetensors").is_file()
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_a_kernel_error_bit_fails_the_requests_of_its_step_and_generation_goes_on(folders, ahead):
+    """The generation path does not synchronise to read the kernels' error word: the word comes with the sampled ids.
+    A bit that stands in it when a step's tokens are read (here put there by hand, as a kernel that met a missing page
+    would) fails that step's requests with a message that names it, gives their pages back and clears the word; the
+    next requests generate what they should. The same with a step launched ahead."""
+    from damendaemon_b200 import kernels
+    from damendaemon_b200.engine.scheduler import Request, Scheduler
+    from damendaemon_b200.runtime import Runtime
+    plain = PlainGpt2(folders["A"])
+    runtime = Runtime(folders["A"], dtype="float32", max_batch=4, page_size=16, run_ahead=ahead)
+    scheduler = Scheduler(runtime.engine, run_ahead=ahead)
+    a = scheduler.submit(Request([5, 17, 3], max_tokens=20, ignore_eos=True))
+    b = scheduler.submit(Request([9, 8], max_tokens=20, ignore_eos=True))
+    for _ in range(4):
+        scheduler.step()
+    assert len(a.output) >= 3 and not a.finished
+    kernels.error_flag(runtime.engine.device).fill_(4)           # "a page was missing on a read"
+    events = []
+    while not (a.finished and b.finished):
+        events += scheduler.step()
+    assert a.finish_reason == b.finish_reason == "error" and "0x4" in a.error and "DeviceStepError" in a.error
+    assert sum(1 for e in events if e.token is None and e.finished) == 2
+    assert runtime.engine.cache.used_tokens == 0 and not runtime.engine.live_requests()
+    assert kernels.read_error_flag(runtime.engine.device) == 0      # the word was cleared
+    assert runtime.generate_batch([[5, 17, 3]], 6, ignore_eos=True) == [plain.greedy([5, 17, 3], 6)]
