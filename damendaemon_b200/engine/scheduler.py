@@ -134,6 +134,7 @@ class Scheduler:
         self._in_flight = None
         self.steps_ahead = 0     # steps whose forward pass was launched before the tokens of the step before were read
         self.waiting = deque()
+        self._known = {}         # id -> request, from submit until its end (one dictionary lookup serves cancel)
         self.prefilling = []     # admitted, prompt not yet wholly in the cache; admission order
         self.decoding = []       # admitted, generating; admission order
         self.done = []
@@ -156,6 +157,9 @@ class Scheduler:
         request.sampler.prepare(request.prompt, vocab)
         request.submitted_at = time.perf_counter()
         request.waiting_since = self.clock()
+        if request.id in self._known:
+            raise ValueError(f"a request with id {request.id!r} is already in the scheduler")
+        self._known[request.id] = request
         self.waiting.append(request)
         return request
 
@@ -164,11 +168,11 @@ class Scheduler:
         ``step()``: whatever the request holds goes back, and that step's events end with its terminal event
         (token None, finish reason 'cancelled'). Returns False if the request is unknown or has ended already.
         Setting the flag is all this does, so another thread may call it while ``step()`` runs."""
-        for known in itertools.chain(self.waiting, self.prefilling, self.decoding):
-            if known is request or known.id == request:
-                known.cancel_requested = True
-                return True
-        return False
+        known = self._known.get(request.id if isinstance(request, Request) else request)
+        if known is None or known.finished or (isinstance(request, Request) and known is not request):
+            return False
+        known.cancel_requested = True
+        return True
 
     def _withdraw(self, events):
         """Apply cancellations and the queue timeout; runs before anything else in a step."""
@@ -352,6 +356,7 @@ class Scheduler:
 
     def _finish(self, request, reason):
         self.engine.finish(request.id)                  # pages go back before the last event is seen
+        self._known.pop(request.id, None)
         request.finish_reason = reason
         request.finished_at = time.perf_counter()
         for group in (self.prefilling, self.decoding):
@@ -366,6 +371,7 @@ class Scheduler:
         """End a request without a token: what it holds goes back first, then its terminal event is queued."""
         if release:
             self.engine.finish(request.id)
+        self._known.pop(request.id, None)
         request.finish_reason, request.error = reason, message
         request.finished_at = time.perf_counter()
         for group in (self.prefilling, self.decoding):
