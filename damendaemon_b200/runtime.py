@@ -12,6 +12,7 @@ from pathlib import Path
 from .engine import Engine
 from .engine.scheduler import Request, Scheduler
 from .sampling import Sampling
+from .text_stream import TextStream, checked_stops
 
 
 class Runtime:
@@ -55,35 +56,47 @@ class Runtime:
 
     # ------------------------------------------------------------------ one request, streamed
     def generate(self, raw_prompt, max_tokens=128, ignore_eos=False, temperature=0, top_p=1, top_k=0, seed=None,
-                 presence_penalty=0, frequency_penalty=0, repetition_penalty=1, logit_bias=None):
-        """Yield ``{"token": id, "text": delta}`` per generated token, then the terminal event."""
+                 presence_penalty=0, frequency_penalty=0, repetition_penalty=1, logit_bias=None, stop=None):
+        """Yield ``{"token": id, "text": delta}`` per generated token, then the terminal event. ``text`` is what has
+        become certain with this token (an unfinished UTF-8 sequence or the beginning of a stop string is held back).
+        ``stop``: one to four strings; generation ends ('stop') where the text first holds one of them, and neither it
+        nor anything after it is handed out (damendaemon/stopping.py:4-41). Stop strings need the folder's tokenizer."""
         if type(max_tokens) is not int or max_tokens <= 0:
             raise ValueError("max_tokens must be a positive integer")
         if max_tokens > self.context:
             raise ValueError("max_tokens exceeds configured context")
         sampling = Sampling(temperature, top_p, top_k, seed, presence_penalty, frequency_penalty, repetition_penalty,
                             logit_bias)
+        stops = checked_stops(stop)
+        if stops and self.tokenizer is None:
+            raise ValueError("stop strings need tokenizer.json in the model folder")
         prompt = self._prompt_ids(raw_prompt)
         if len(prompt) + max_tokens > self.context:
             raise ValueError("prompt plus max_tokens exceeds configured context")
         start = time.perf_counter()
         scheduler = self._scheduler()
         request = scheduler.submit(Request(prompt, max_tokens, sampling, ignore_eos))
-        emitted, first = "", None
+        stream, first, stopped_at = TextStream(stops), None, None
         try:
             for event in scheduler.run():
                 if event.token is None:
+                    if request.finish_reason == "cancelled":
+                        break                               # withdrawn below, after a stop string
                     raise RuntimeError(request.error)
+                if stopped_at is not None:
+                    continue                                # a token of a step that was in flight when the text stopped
                 if first is None:
                     first = time.perf_counter() - start
-                text = self._text(request.output)
-                delta, emitted = text[len(emitted):], text
+                delta, stopped = stream.push(self._text(request.output), final=event.finished)
+                if stopped:
+                    stopped_at = len(request.output)
+                    scheduler.cancel(request)               # pages back at the next step; no further token is handed out
                 yield {"token": event.token, "text": delta}
         finally:
             self.engine.finish(request.id)
         elapsed = time.perf_counter() - start
-        n = len(request.output)
-        yield {"finish_reason": request.finish_reason,
+        n = stopped_at if stopped_at is not None else len(request.output)
+        yield {"finish_reason": "stop" if stopped_at is not None else request.finish_reason,
                "usage": {"prompt_tokens": len(prompt), "completion_tokens": n, "total_tokens": len(prompt) + n},
                "timing": {"kernel_backend": "cuda-sm100a", "compute_dtype": str(self.engine.dtype).removeprefix("torch."),
                           "first_token_seconds": first, "total_seconds": elapsed,

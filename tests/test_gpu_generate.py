@@ -207,3 +207,38 @@ def test_a_kernel_error_bit_fails_the_requests_of_its_step_and_generation_goes_o
     assert runtime.engine.cache.used_tokens == 0 and not runtime.engine.live_requests()
     assert kernels.read_error_flag(runtime.engine.device) == 0      # the word was cleared
     assert runtime.generate_batch([[5, 17, 3]], 6, ignore_eos=True) == [plain.greedy([5, 17, 3], 6)]
+
+
+def test_stop_strings_and_text_deltas(folders, tmp_path):
+    """With a tokenizer in the folder ``generate`` hands out text: a stop string that completes in the middle of the
+    generation ends it there ('stop'), nothing of the stop string or after it is shown, the request's pages go back,
+    and the pieces of text add up to what was decoded before the stop."""
+    import shutil
+    from damendaemon_b200.runtime import Runtime
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(folders["A"], folder)
+    vocab = {f"w{i}": i for i in range(TINY_A["vocab_size"])}
+    (folder / "tokenizer.json").write_text(json.dumps({
+        "version": "1.0", "truncation": None, "padding": None, "added_tokens": [], "normalizer": None,
+        "pre_tokenizer": {"type": "Whitespace"}, "post_processor": None, "decoder": None,
+        "model": {"type": "WordLevel", "vocab": vocab, "unk_token": "w0"}}))
+    runtime = Runtime(folder, dtype="float32", max_batch=2, page_size=16)
+    assert runtime.tokenizer is not None
+    prompt = "w5 w17 w3 w200"
+    free = list(runtime.generate(prompt, 10, ignore_eos=True))
+    tokens = [e["token"] for e in free[:-1]]
+    assert tokens == PlainGpt2(folders["A"]).greedy([5, 17, 3, 200], 10) and free[-1]["finish_reason"] == "length"
+    assert "".join(e["text"] for e in free[:-1]) == " ".join(f"w{t}" for t in tokens)
+    k = next(i for i in range(2, 9) if tokens[i] not in tokens[:i])      # a word that has not come before
+    stop = f"w{tokens[k]} "                                  # complete once the next token's word follows it
+    events = list(runtime.generate(prompt, 10, ignore_eos=True, stop=[stop, "never"]))
+    final = events[-1]
+    shown = "".join(e["text"] for e in events[:-1])
+    assert final["finish_reason"] == "stop" and final["usage"]["completion_tokens"] == k + 2
+    assert [e["token"] for e in events[:-1]] == tokens[:k + 2]
+    assert shown == "".join(f"w{t} " for t in tokens[:k]) and stop not in shown
+    assert runtime.engine.cache.used_tokens == 0 and not runtime.engine.live_requests()
+    with pytest.raises(ValueError, match="stop"):
+        list(runtime.generate(prompt, 4, stop=[""]))
+    with pytest.raises(ValueError, match="tokenizer"):
+        list(Runtime(folders["A"], dtype="float32", max_batch=1).generate([5, 17], 4, stop="x"))
