@@ -43,6 +43,22 @@ TINY_D = {
 }
 
 
+# head size 128: in bfloat16 the mma.sync prompt kernel and the row decode kernel at the engine's level
+TINY_E = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 256, "n_head": 2, "n_inner": 384, "vocab_size": 411, "n_positions": 192,
+    "layer_norm_epsilon": 1e-5, "activation_function": "gelu",
+    "scale_attn_by_inverse_layer_idx": False,
+}
+# head size 80 (a step of 16 that no tensor-core attention kernel takes): the general kernel in both dtypes; seven heads
+TINY_F = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 1, "n_embd": 560, "n_head": 7, "n_inner": 600, "vocab_size": 257, "n_positions": 80,
+    "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_by_inverse_layer_idx": True,
+}
+
+
 @pytest.fixture(scope="session")
 def tiny_configs():
     return {"A": dict(TINY_A), "B": dict(TINY_B)}

@@ -4,7 +4,7 @@ so few pages that they are used again."""
 import pytest
 import torch
 
-from conftest import TINY_A, TINY_B, TINY_C, TINY_D
+from conftest import TINY_A, TINY_B, TINY_C, TINY_D, TINY_E, TINY_F
 from model_tools import make_model, random_requests
 from plain_gpt2 import PlainGpt2
 from trace_tools import mixed_steps, portion_steps, run_trace, tail_steps, whole_steps
@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 
 # name: (config, seed, request lengths, factor on the QKV projection that makes attention peaky)
 CASES = {"A": (TINY_A, 0, [5, 17, 33, 100, 128, 64], 8.0), "B": (TINY_B, 1, [1, 9, 64, 200, 256, 77], 8.0),
-         "C": (TINY_C, 2, [1, 70, 320, 129, 64, 200], 3.0), "D": (TINY_D, 3, [3, 40, 96, 17, 65], 8.0)}
+         "C": (TINY_C, 2, [1, 70, 320, 129, 64, 200], 3.0), "D": (TINY_D, 3, [3, 40, 96, 17, 65], 8.0),
+         "E": (TINY_E, 4, [2, 130, 192, 65, 31], 2.0), "F": (TINY_F, 5, [1, 80, 33, 17, 64, 80, 48, 70], 1.0)}
 # float32: the engine's contract. bfloat16: three times what rounding the stored activations to
 # bfloat16 does to the plain implementation's own logits for that model (measured in the fixture,
 # about 0.005 for these models), plus a small floor.
@@ -79,11 +80,11 @@ def compare(got, want, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cuttings(models, name, dtype, mode):
     folder, config, requests, want = models[name, dtype]
-    page = {"A": 16, "B": 8, "C": 16, "D": 32}[name]
+    page = {"A": 16, "B": 8, "C": 16, "D": 32, "E": 64, "F": 16}[name]
     if mode == "mixed":
         builder, peak = mixed_steps(requests, seed=3)
         kv = peak
