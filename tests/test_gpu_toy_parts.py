@@ -65,6 +65,7 @@ class RotarySpec:
     kind: str
     head_dim: int
     base: float
+    in_place: bool = True      # False: hand back new tensors instead (the framework then packs q, k, v again)
 
 
 class Rotary(PositionEncoding):
@@ -78,10 +79,15 @@ class Rotary(PositionEncoding):
         freq = self.spec.base ** (-torch.arange(0, d // 2, device=q.device, dtype=torch.float32) * 2 / d)
         angle = ctx.positions.float()[:, None] * freq[None, :]
         cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        turned = []
         for t in (q, k):
             x = t.reshape(t.shape[0], -1, d).float()
             a, b = x[..., :d // 2], x[..., d // 2:]
-            t.copy_(torch.cat([a * cos - b * sin, b * cos + a * sin], -1).reshape(t.shape).to(t.dtype))
+            turned.append(torch.cat([a * cos - b * sin, b * cos + a * sin], -1).reshape(t.shape).to(t.dtype))
+        if not self.spec.in_place:
+            return turned[0], turned[1]
+        q.copy_(turned[0])
+        k.copy_(turned[1])
         return q, k
 
 
@@ -107,6 +113,7 @@ class ToyMixConfig:
     vocab: int = 173
     positions: int = 96
     window: int = 11
+    rotate_in_place: bool = True
 
     def to_dict(self):
         return {"architectures": ["ToyMixLM"], **self.__dict__}
@@ -126,7 +133,7 @@ def toy_spec(c):
                   (norm("l1.n"),)),
     )
     return ModelSpec("ToyMixLM", c.vocab, c.width, c.positions, EmbeddingSpec("tokens", c.vocab, c.width, "embed.weight"),
-                     RotarySpec("toy_rotary", d, 100.0), layers, (RunEntry(0), RunEntry(1)),
+                     RotarySpec("toy_rotary", d, 100.0, c.rotate_in_place), layers, (RunEntry(0), RunEntry(1)),
                      HeadSpec("linear", c.vocab, c.width, norm("final"), "head.weight", bias="head.bias"))
 
 
@@ -187,15 +194,16 @@ def toy_plain(c, w, ids, rounded=None):
     return ln(x, "final") @ w["head.weight"].t() + w["head.bias"]
 
 
+@pytest.mark.parametrize("in_place", [True, False])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_architecture_of_outside_parts(dtype):
+def test_toy_architecture_of_outside_parts(dtype, in_place):
     from damendaemon_b200.engine import Engine, StepEntry
     register_feed_forward("toy_routed", RoutedFeedForward, replace=True)
     register_position("toy_rotary", Rotary, replace=True)
     register_arrangement("toy_parallel", ParallelBlock, replace=True)
     register_architecture(Architecture("ToyMixLM", lambda raw: ToyMixConfig(**{k: v for k, v in raw.items() if k != "architectures"}),
                                        toy_spec, lambda c, seed, dt=torch.float32, device="cpu": toy_tensors(c, seed, dt)), replace=True)
-    c = ToyMixConfig()
+    c = ToyMixConfig(rotate_in_place=in_place)
     tensors = toy_tensors(c, 17, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
     engine = Engine(config=c.to_dict(), tensors=tensors, dtype=dtype, kv_tokens=160, page_size=8, max_requests=3)
     # two cache groups: all keys for layer 0, a window of them for layer 1, each with pages of its own
