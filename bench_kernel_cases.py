@@ -39,6 +39,17 @@ def _gemm_case(name, tokens, dev):
     return run, work
 
 
+def _layernorm_case(rows, dev):
+    """LayerNorm of `rows` rows of the float32 stream (width 1600) into bfloat16, as before every projection."""
+    width = H * D
+    copies = max(2, min(24, (300 << 20) // (rows * width * 4)))
+    xs = [torch.randn(rows, width, device=dev) for _ in range(copies)]
+    gamma, beta = torch.ones(width, device=dev), torch.zeros(width, device=dev)
+    out = torch.empty(rows, width, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.layernorm(xs[i % copies], gamma, beta, 1e-5, torch.bfloat16, out=out)
+    return run, {"bytes": rows * width * 6, "flops": 8 * rows * width}
+
+
 def _cache_case(batch, context, dev, copies):
     n_pages = batch * ((context + PAGE - 1) // PAGE)
     caches = [torch.randn(n_pages, 2, H, PAGE, D, device=dev).to(torch.bfloat16) for _ in range(copies)]
@@ -73,11 +84,13 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False):
 
 def build(name, device="cuda:0"):
     """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> (page streaming) | attn_decode_rows_b<batch> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
-    attn_prefill_long (one prompt of 4,096 tokens)"""
+    attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows>"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
         return _gemm_case(parts[1], int(parts[2][1:]), device)
+    if name.startswith("layernorm_m"):
+        return _layernorm_case(int(name[len("layernorm_m"):]), device)
     if name.startswith("attn_decode_rows_b"):
         return _decode_case(int(name[len("attn_decode_rows_b"):]), 768, device, kernel="rows")
     if name.startswith("attn_decode_b"):

@@ -651,6 +651,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         const int quarter = warp & 3;
         // the two warps of a lane quarter split the tile's features in halves (in chunks of 16)
         constexpr int FIRST_HALF = ((BN / 16 + 1) / 2) * 16;
+        constexpr int CHUNKS = FIRST_HALF / 16;       // chunks of 16 features a warp finishes of a tile, at most
+        constexpr int AHEAD = CHUNKS < 3 ? CHUNKS : 3;
         const int c_begin = warp >= 6 ? FIRST_HALF : 0;
         const int c_limit = warp >= 6 ? BN : FIRST_HALF;
         uint32_t local = 0;
@@ -659,6 +661,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             const uint32_t acc = local & 1;
             const int m = a0 + quarter * 32 + lane;
             const bool m_ok = m < p.M;
+            // The residual is an earlier kernel's data (or an earlier tile's own rows elsewhere): the first AHEAD chunks of
+            // this thread's piece of its row are asked for now, while the MMAs of the tile still run, and each later
+            // chunk while the chunk AHEAD before it is finished; read chunk by chunk when the accumulator is there, a
+            // warp paid a trip to memory six or eight times a tile.
+            float res[AHEAD][16];
+            if (p.residual) {
+#pragma unroll
+                for (int ci = 0; ci < AHEAD; ++ci) {
+                    const int c0 = c_begin + ci * 16;
+                    if (m_ok && c0 < c_limit && b0 + c0 < p.N) load_residual_row16(p, m, b0 + c0, res[ci]);
+                }
+            }
             if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*epilogue_abort) break;
@@ -669,22 +683,41 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 __syncwarp();
                 if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
             }
-            for (int c0 = c_begin; c0 < c_limit && b0 + c0 < p.N; c0 += 16) {
-                uint32_t r[16];
-                tc::tmem_ld_x16(lane_addr + c0, r);
-                float res[16];
-                float bias16[16];
-                if (m_ok) {                                           // in flight while the accumulator is read
-                    load_residual_row16(p, m, b0 + c0, res);
-                    load_bias16(p, b0 + c0, bias16);
+            if (p.residual) {
+#pragma unroll
+                for (int ci = 0; ci < CHUNKS; ++ci) {
+                    const int c0 = c_begin + ci * 16;
+                    if (c0 >= c_limit || b0 + c0 >= p.N) break;
+                    uint32_t r[16];
+                    tc::tmem_ld_x16(lane_addr + c0, r);
+                    float bias16[16];
+                    if (m_ok) load_bias16(p, b0 + c0, bias16);
+                    tc::tmem_ld_wait();
+                    if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
+                        tc::fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
+                    }
+                    if (m_ok) store_out_row16(p, m, b0 + c0, r, res[ci % AHEAD], bias16);
+                    // the residual of the chunk AHEAD further on, into the registers this chunk has just given up
+                    const int c_next = c0 + AHEAD * 16;
+                    if (ci + AHEAD < CHUNKS && m_ok && c_next < c_limit && b0 + c_next < p.N)
+                        load_residual_row16(p, m, b0 + c_next, res[ci % AHEAD]);
                 }
-                tc::tmem_ld_wait();
-                if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
-                    tc::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
+            } else {
+                for (int c0 = c_begin; c0 < c_limit && b0 + c0 < p.N; c0 += 16) {
+                    uint32_t r[16];
+                    tc::tmem_ld_x16(lane_addr + c0, r);
+                    float bias16[16];
+                    if (m_ok) load_bias16(p, b0 + c0, bias16);          // in flight while the accumulator is read
+                    tc::tmem_ld_wait();
+                    if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
+                        tc::fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(&tmem_empty_bar[acc], 0));
+                    }
+                    if (m_ok) store_out_row16(p, m, b0 + c0, r, bias16, bias16);    // no residual: the second argument is not read
                 }
-                if (m_ok) store_out_row16(p, m, b0 + c0, r, res, bias16);
             }
         }
     }
