@@ -553,6 +553,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                          const GemmParams p) {
     using C = PairConfig<BN>;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(16) float bias_s[2][256];        // the bias of a tile's features, tiles alternating
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);   // used in the leader only
     uint64_t* empty_bar = full_bar + C::STAGES;
@@ -604,6 +605,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         if (tc::elect_one()) {
             tc::prefetch_tensormap(&map_w);
             tc::prefetch_tensormap(&map_x);
+            // Weights do not depend on the kernel before this one: the weight halves of the first tile's first stages
+            // are on their way before the wait; the activations follow after it.
+            int ahead = 0;
+            if (pair < n_items) {
+                const int b_first = (pair / tiles_a) * BN;
+                ahead = min(n_kblocks, C::STAGES);
+                for (int i = 0; i < ahead; ++i) {
+                    if (rank == 0) tc::mbar_expect_tx(&full_bar[i], 2 * C::STAGE_BYTES);     // both blocks' bytes
+                    tc::tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_w, i * BK, b_first + (int)rank * C::HALF,
+                                         tc::map_to_rank(&full_bar[i], 0));
+                }
+            }
             dd_grid_wait();
             uint32_t it = 0;
             bool ok = true;
@@ -611,11 +624,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 DD_PAIR_COORDS(item)
                 for (int i = 0; i < n_kblocks; ++i, ++it) {
                     const int s = it % C::STAGES;
-                    if (!tc::mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* a_dst = tiles + s * C::STAGE_BYTES;
                     uint8_t* b_dst = a_dst + C::A_BYTES;
-                    if (rank == 0) tc::mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);     // both blocks' bytes
                     const uint32_t leader_full = tc::map_to_rank(&full_bar[s], 0);
+                    if ((int)it < ahead) {                 // the weight half of this stage is already on its way
+                        tc::tma_load_2d_pair(a_dst, &map_x, i * BK, a0, leader_full);
+                        continue;
+                    }
+                    if (!tc::mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    if (rank == 0) tc::mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);     // both blocks' bytes
                     tc::tma_load_2d_pair(a_dst, &map_x, i * BK, a0, leader_full);
                     tc::tma_load_2d_pair(b_dst, &map_w, i * BK, b0 + (int)rank * C::HALF, leader_full);
                 }
@@ -661,6 +678,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             const uint32_t acc = local & 1;
             const int m = a0 + quarter * 32 + lane;
             const bool m_ok = m < p.M;
+            // The bias of the tile's features is a weight: the eight warps put it into shared memory while the MMAs run
+            // (a chunk that asked L2 for it just before it was needed waited for the answer, six or eight times a tile).
+            float* bias_tile = bias_s[local & 1];
+            {
+                const int f = (int)threadIdx.x - 64;
+                if (f < BN) bias_tile[f] = (p.bias && b0 + f < p.N) ? __ldg(p.bias + b0 + f) : 0.f;
+            }
             // The residual is an earlier kernel's data (or an earlier tile's own rows elsewhere): the first AHEAD chunks of
             // this thread's piece of its row are asked for now, while the MMAs of the tile still run, and each later
             // chunk while the chunk AHEAD before it is finished; read chunk by chunk when the accumulator is there, a
@@ -691,7 +715,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
                     float bias16[16];
-                    if (m_ok) load_bias16(p, b0 + c0, bias16);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias_tile + c0 + 4 * q);
+                        bias16[4 * q] = b4.x; bias16[4 * q + 1] = b4.y; bias16[4 * q + 2] = b4.z; bias16[4 * q + 3] = b4.w;
+                    }
                     tc::tmem_ld_wait();
                     if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
                         tc::fence_before_sync();
@@ -709,7 +737,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
                     float bias16[16];
-                    if (m_ok) load_bias16(p, b0 + c0, bias16);          // in flight while the accumulator is read
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias_tile + c0 + 4 * q);
+                        bias16[4 * q] = b4.x; bias16[4 * q + 1] = b4.y; bias16[4 * q + 2] = b4.z; bias16[4 * q + 3] = b4.w;
+                    }
                     tc::tmem_ld_wait();
                     if (c0 + 16 >= c_limit || b0 + c0 + 16 >= p.N) {      // this warp's last read: hand it back to the leader
                         tc::fence_before_sync();
