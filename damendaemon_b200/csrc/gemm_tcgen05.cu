@@ -283,6 +283,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     using C = Config<BN>;
     constexpr bool BY_TOKEN = C::BY_TOKEN;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(16) float bias_s[2][256];        // tiles of tokens: the bias of a tile's features, tiles alternating
     // the swizzled tiles need 1024-byte alignment
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
@@ -415,6 +416,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;
         // the two warps of a lane quarter split the tile's columns in halves (in chunks of 16)
         constexpr int FIRST_HALF = ((BN / 16 + 1) / 2) * 16;
+        constexpr int CHUNKS = FIRST_HALF / 16 < 1 ? 1 : FIRST_HALF / 16;   // chunks of 16 columns a warp finishes of a tile, at most
+        constexpr int AHEAD = CHUNKS < 3 ? CHUNKS : 3;
         const int c_begin = warp >= 6 ? FIRST_HALF : 0;
         const int c_limit = warp >= 6 ? BN : FIRST_HALF;
         uint32_t local = 0;
@@ -426,6 +429,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool row_ok = row < rows_a;
             // the bias of this thread's feature is a weight: it is on its way before the accumulator is waited for
             const float feature_bias = (!BY_TOKEN && row_ok && p.bias) ? __ldg(p.bias + row) : 0.f;
+            // Tiles of tokens: the bias of the tile's features goes to shared memory, and the first chunks of this thread's
+            // piece of the residual row into registers, while the MMAs of the tile still run (see the two-SM kernel).
+            float* bias_tile = bias_s[local & 1];
+            float res_ahead[AHEAD][16];
+            if (BY_TOKEN && p.splits == 1) {
+                const int f = (int)threadIdx.x - 64;
+                if (f < BN) bias_tile[f] = (p.bias && b0 + f < p.N) ? __ldg(p.bias + b0 + f) : 0.f;
+                if (p.residual) {
+#pragma unroll
+                    for (int ci = 0; ci < AHEAD; ++ci) {
+                        const int c0 = c_begin + ci * 16;
+                        if (row_ok && c0 < c_limit && b0 + c0 < rows_b) load_residual_row16(p, row, b0 + c0, res_ahead[ci]);
+                    }
+                }
+            }
             if (!tc::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1, abort_flag)) *epilogue_abort = 1;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*epilogue_abort) break;                   // the same decision in all eight warps
@@ -436,15 +454,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 __syncwarp();
                 if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
             }
-            if (p.splits == 1) {
+            if (BY_TOKEN && p.splits == 1 && p.residual) {
+#pragma unroll
+                for (int ci = 0; ci < CHUNKS; ++ci) {
+                    const int c0 = c_begin + ci * 16;
+                    if (c0 >= c_limit || b0 + c0 >= rows_b) break;
+                    uint32_t r[16];
+                    tc::tmem_ld_x16(lane_addr + c0, r);
+                    float bias16[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias_tile + c0 + 4 * q);
+                        bias16[4 * q] = b4.x; bias16[4 * q + 1] = b4.y; bias16[4 * q + 2] = b4.z; bias16[4 * q + 3] = b4.w;
+                    }
+                    tc::tmem_ld_wait();
+                    if (c0 + 16 >= c_limit || b0 + c0 + 16 >= rows_b) {  // this warp's last read of the accumulator
+                        tc::fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) tc::mbar_arrive(&tmem_empty_bar[acc]);
+                    }
+                    if (row_ok) store_out_row16(p, row, b0 + c0, r, res_ahead[ci % AHEAD], bias16);
+                    const int c_next = c0 + AHEAD * 16;
+                    if (ci + AHEAD < CHUNKS && row_ok && c_next < c_limit && b0 + c_next < rows_b)
+                        load_residual_row16(p, row, b0 + c_next, res_ahead[ci % AHEAD]);
+                }
+            } else if (p.splits == 1) {
                 for (int c0 = c_begin; c0 < c_limit && b0 + c0 < rows_b; c0 += 16) {
                     uint32_t r[16];
                     tc::tmem_ld_x16(lane_addr + c0, r);
                     float res[16], bias16[16];
                     if (row_ok) {                                        // in flight while the accumulator is read
-                        if (BY_TOKEN) {
-                            load_residual_row16(p, row, b0 + c0, res);
-                            load_bias16(p, b0 + c0, bias16);
+                        if (BY_TOKEN) {                                  // no residual on this path
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 b4 = *reinterpret_cast<const float4*>(bias_tile + c0 + 4 * q);
+                                bias16[4 * q] = b4.x; bias16[4 * q + 1] = b4.y; bias16[4 * q + 2] = b4.z; bias16[4 * q + 3] = b4.w;
+                            }
                         } else load_residual16(p, b0 + c0, row, res);
                     }
                     tc::tmem_ld_wait();
