@@ -92,8 +92,13 @@ class Engine:
         self.check_device_errors = check_device_errors
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_graph = use_graph and self.model.graph_safe
-        self._graphs, self._seen = {}, set()
+        self._graphs, self._seen = {}, {}
         self.graph_replays = 0                          # steps that ran as a replay of a captured graph
+        self.graph_captures = 0
+        # A capture costs about ten eager steps' worth of host time, so a shape must come back before it is captured:
+        # decode-only shapes (which then recur for hundreds of steps) at their second appearance, shapes with prompt
+        # portions (whose token counts seldom repeat exactly) at their fourth.
+        self.capture_after = {True: 1, False: 3}        # decode only? -> appearances before the capturing one
         self.max_graphs = 48                            # replayable step shapes kept; the least recently used goes first
         self.max_graph_tokens = 4096                    # larger steps run eagerly (a graph keeps its activations)
         kernels.error_flag(self.device)                 # allocated before any graph capture
@@ -287,8 +292,8 @@ class Engine:
             # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.
             key = (N, E, M, decode_only, aligned)
             graph = self._graphs.get(key)
-            if graph is None and key in self._seen:
-                # the second step of this shape: capture it (the first ran eagerly and warmed everything up)
+            if graph is None and self._seen.get(key, 0) >= self.capture_after[decode_only]:
+                # this shape has come back often enough: capture it (its first run was eager and warmed everything up)
                 ctx = self._context(N, E, M, at, decode_only, self.max_context, aligned=aligned)
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.current_stream().synchronize()
@@ -297,12 +302,15 @@ class Engine:
                 while len(self._graphs) >= self.max_graphs:
                     self._graphs.pop(next(iter(self._graphs)))
                 self._graphs[key] = graph = (graph, static_logits)
+                self.graph_captures += 1
             if graph is not None:
                 self._graphs[key] = self._graphs.pop(key)        # most recently used last
                 graph[0].replay()
                 self.graph_replays += 1
                 return graph[1]             # valid until the next step of this shape
-            self._seen.add(key)
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if len(self._seen) > 4096:                   # shapes that never came back
+                self._seen = {k: n for k, n in self._seen.items() if n > 1}
         ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
         return self.model.forward(ctx, self._caches)
 

@@ -30,6 +30,7 @@ def test_replayed_prompt_and_mixed_steps(model_c, dtype):
     vocab = TINY_C["vocab_size"]
     g = torch.Generator().manual_seed(9)
     engine = Engine(folder, dtype=dtype, kv_tokens=1024, page_size=16, max_requests=8, use_graph=True)
+    engine.capture_after = {True: 1, False: 1}      # every shape is captured when it comes back for the first time
     for group in engine.cache.groups:
         group.arena.fill_(float("nan"))
     # (first portions, second portions, a newcomer's prompt): each trial has the counts of the others
