@@ -297,7 +297,7 @@ class Engine:
                 ctx = self._context(N, E, M, at, decode_only, self.max_context, aligned=aligned)
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.current_stream().synchronize()
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph), kernels.stream_scope():
                     static_logits = self.model.forward(ctx, self._caches)
                 while len(self._graphs) >= self.max_graphs:
                     self._graphs.pop(next(iter(self._graphs)))
@@ -312,7 +312,8 @@ class Engine:
             if len(self._seen) > 4096:                   # shapes that never came back
                 self._seen = {k: n for k, n in self._seen.items() if n > 1}
         ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
-        return self.model.forward(ctx, self._caches)
+        with kernels.stream_scope():
+            return self.model.forward(ctx, self._caches)
 
     accepts_device_ids = True          # step() can take the token ids of a decode step from a device tensor
 

@@ -57,7 +57,7 @@ from .engine import StepEntry
 _ids = itertools.count()
 
 
-@dataclass
+@dataclass(eq=False)          # a request is itself, not its fields: membership tests must not compare prompts
 class Request:
     prompt: list
     max_tokens: int = 128

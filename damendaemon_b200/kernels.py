@@ -106,8 +106,27 @@ def _call(lib, fn, *args, n_kernels=1):
         raise KernelError(lib.dd_last_error().decode())
 
 
+_scoped_stream = None
+
+
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    return _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class stream_scope:
+    """Every kernel launched inside the scope goes to the stream that was current when the scope was entered, looked
+    up once: asking torch for the current stream costs a few microseconds, and a step launches hundreds of kernels.
+    (Enter it inside a graph capture, not around it: the capture switches streams.)"""
+
+    def __enter__(self):
+        global _scoped_stream
+        self.outer, _scoped_stream = _scoped_stream, torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self.outer
+        return False
 
 
 def _dt(t):
