@@ -242,3 +242,42 @@ def test_stop_strings_and_text_deltas(folders, tmp_path):
         list(runtime.generate(prompt, 4, stop=[""]))
     with pytest.raises(ValueError, match="tokenizer"):
         list(Runtime(folders["A"], dtype="float32", max_batch=1).generate([5, 17], 4, stop="x"))
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+@pytest.mark.parametrize("ahead", [False, True])
+def test_random_arrivals_and_cancellations_generate_what_plain_does(folders, seed, ahead):
+    """Requests arrive between steps, a pool of few pages makes some wait, some are withdrawn at random moments (while
+    waiting, between portions of their prompt, while decoding, with a step launched ahead): every request that runs to
+    its end has the plain implementation's greedy tokens, every withdrawn one a beginning of them, and nothing is left
+    in the cache. float32, so that the tokens are the plain ones exactly."""
+    from damendaemon_b200.engine.scheduler import Request, Scheduler
+    from damendaemon_b200.runtime import Runtime
+    plain = PlainGpt2(folders["A"])
+    rng = random.Random(seed)
+    runtime = Runtime(folders["A"], dtype="float32", max_batch=3, page_size=16, kv_cache_tokens=160, run_ahead=ahead)
+    scheduler = Scheduler(runtime.engine, token_budget=24, chunk_size=16, run_ahead=ahead)
+    arrivals = sorted(rng.randrange(0, 30) for _ in range(10))
+    requests, cancelled, step = [], set(), 0
+    while arrivals or not scheduler.idle:
+        while arrivals and arrivals[0] <= step:
+            arrivals.pop(0)
+            prompt = [rng.randrange(0, TINY_A["vocab_size"]) for _ in range(rng.randrange(1, 40))]
+            requests.append(scheduler.submit(Request(prompt, max_tokens=rng.randrange(1, 14), ignore_eos=True)))
+        if requests and rng.random() < 0.15:
+            victim = rng.choice(requests)
+            if scheduler.cancel(victim):
+                cancelled.add(victim.id)
+        scheduler.step()
+        runtime.engine.cache.check()
+        step += 1
+        assert step < 1000
+    assert cancelled, "no request was withdrawn: the test shows nothing about cancellation"
+    for r in requests:
+        want = plain.greedy(r.prompt, r.max_tokens)
+        if r.id in cancelled and r.finish_reason == "cancelled":
+            assert r.output == want[:len(r.output)] and len(r.output) < len(want)
+        else:
+            assert r.finish_reason == "length" and r.output == want, (r.id, r.finish_reason)
+    assert runtime.engine.cache.used_tokens == 0 and not runtime.engine.live_requests()
+    assert runtime.engine.cache.groups[0].pool.unpromised_pages == runtime.engine.cache.groups[0].pool.n_pages
