@@ -176,12 +176,12 @@ def decode_end_to_end(runtime, batch, warmup, steps, vocab):
     return produced / wall, h2d, (batch + 1) * 4     # the sampled ids and the kernels' error word
 
 
-def prefill_timed(engine, vocab, repeats=5):
+def prefill_timed(engine, vocab, repeats=5, prompts=2, length=1024):
     import torch
     from damendaemon_b200.engine import StepEntry
     times = []
     for rep in range(2 + repeats):
-        entries = [StepEntry(f"p{rep}-{i}", random_ids(1024, vocab, 7 + i + 10 * rep), [1023]) for i in range(2)]
+        entries = [StepEntry(f"p{rep}-{i}", random_ids(length, vocab, 7 + i + 10 * rep), [length - 1]) for i in range(prompts)]
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -417,6 +417,15 @@ def main():
                 points["decode_b64_ctx1000_hbm_frac"] = round(long_bytes / (long_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
             del rt
             torch.cuda.empty_cache()
+        # a longer prefill than the model's own positions allow: the same layers with a position table of 4,096 rows
+        # (a bench-only configuration), four prompts of 4,096 tokens in one step
+        long_config = {**config, "n_positions": 4096}
+        rt = make_runtime(long_config, 4, use_graph=False)
+        long_ms = prefill_timed(rt.engine, vocab, repeats=3, prompts=4, length=4096)
+        points["prefill_4x4096"] = round(4 * 4096 * 1000.0 / long_ms, 1)
+        points["prefill_4x4096_frac"] = round(prefill_flops(long_config, layers, 4096, 4) / (long_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)
+        del rt
+        torch.cuda.empty_cache()
         if layers == XL["n_layer"]:
             for name in sorted(WORKLOADS):          # the scheduler under mixed loads (generated tokens a second)
                 points[f"workload_{name}"] = run_workload(name)["value"]
