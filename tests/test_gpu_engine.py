@@ -204,3 +204,24 @@ def test_trace_run_program(models, dtype, tmp_path):
     outputs = run_trace(folder, dtype, builder.steps, tmp_path / "out", max_tokens=peak, page_size=16)
     got = {r: {p: torch.from_numpy(row.copy()) for p, row in rows.items()} for r, rows in builder.collect(outputs).items()}
     compare(got, want, TOL["A", dtype], f"trace_run {dtype}")
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16"), ("E", "bfloat16"), ("B", "bfloat16")])
+def test_random_traces_with_graphs_on(models, name, dtype, seed):
+    """Random mixed traces (other seeds, other numbers of live requests, other portion sizes than the fixed ones above)
+    through an engine that captures every step shape when it comes back and replays it from then on, with a pool so
+    small that pages are used again: every position against the plain implementation."""
+    from damendaemon_b200.engine import Engine
+    folder, config, requests, want = models[name, dtype]
+    page = {"A": 16, "B": 8, "C": 16, "E": 64}[name]
+    portions = [(2, 3, 5, 8, 13, 17, 32), (1, 2, 64), (16, 128, 130), (4, 4, 4, 31)][seed % 4]
+    builder, peak = mixed_steps(requests, seed=100 + seed, max_live=2 + seed % 3, prompt_share=0.3 + 0.1 * (seed % 5), portions=portions)
+    engine = Engine(folder, dtype=dtype, kv_tokens=peak, page_size=page, max_requests=8, use_graph=True)
+    engine.capture_after = {True: 1, False: 1}
+    for g in engine.cache.groups:
+        g.arena.fill_(float("nan"))
+    got = replay(engine, builder)
+    compare(got, want, TOL[name, dtype], f"{name} {dtype} random trace {seed}")
+    assert engine.cache.used_tokens == 0 and not engine.live_requests()
+    assert engine.raise_device_errors() is None
