@@ -83,7 +83,7 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False):
 
 
 def build(name, device="cuda:0"):
-    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch> (page streaming) | attn_decode_rows_b<batch> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch>[_c<context>] (page streaming) | attn_decode_rows_b<batch>[_c<context>] | attn_prefill_p<prompts>_t<tokens> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
     attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows>"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
@@ -91,10 +91,15 @@ def build(name, device="cuda:0"):
         return _gemm_case(parts[1], int(parts[2][1:]), device)
     if name.startswith("layernorm_m"):
         return _layernorm_case(int(name[len("layernorm_m"):]), device)
-    if name.startswith("attn_decode_rows_b"):
-        return _decode_case(int(name[len("attn_decode_rows_b"):]), 768, device, kernel="rows")
-    if name.startswith("attn_decode_b"):
-        return _decode_case(int(name[len("attn_decode_b"):]), 768, device)
+    if name.startswith("attn_decode_rows_b") or name.startswith("attn_decode_b"):
+        # attn_decode[_rows]_b<batch>[_c<context>]: the context is 768 keys unless it is given
+        rows = name.startswith("attn_decode_rows_b")
+        numbers = name[len("attn_decode_rows_b" if rows else "attn_decode_b"):].split("_c")
+        return _decode_case(int(numbers[0]), int(numbers[1]) if len(numbers) > 1 else 768, device, kernel="rows" if rows else "pages")
+    if name.startswith("attn_prefill_p"):
+        # attn_prefill_p<prompts>_t<tokens>: whole prompts of that many tokens
+        prompts, tokens = name[len("attn_prefill_p"):].split("_t")
+        return _prefill_case(int(prompts), int(tokens), device)
     if name == "attn_prefill":
         return _prefill_case(2, 1024, device)
     if name == "attn_prefill_store":
