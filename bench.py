@@ -313,6 +313,16 @@ def parity(layers):
             "logit_scale": float(max(v.abs().max() for v in want.values()))}
 
 
+def line_config(layers, batch, cuda_graph=True):
+    """What both arms run, in the same words (the `config` of the bench line, flat): every size of the model, the batch,
+    the lengths. What only one arm can say of itself (page size, timing method) is under `engine`."""
+    return {"model": "gpt2-xl-shape", "n_layer": XL["n_layer"], "n_layer_run": layers, "n_embd": XL["n_embd"], "n_head": XL["n_head"],
+            "head_dim": XL["n_embd"] // XL["n_head"], "n_inner": XL["n_inner"], "vocab_size": XL["vocab_size"],
+            "n_positions": XL["n_positions"], "global_batch": batch, "seq_len": XL["n_positions"], "prompt_len": PROMPT,
+            "activation": XL["activation_function"], "parallelism": "single-gpu",
+            "l2": "inputs>L2 (every weight is read once a step)", "cuda_graph": cuda_graph}
+
+
 def reference_arm(args):
     """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
     ref = ROOT / "baseline" / "_ref"
@@ -327,7 +337,11 @@ def reference_arm(args):
             config = dict(XL)
             if args.layers:
                 config["n_layer"] = args.layers
-            print(json.dumps(run_reference.run(args, config, PROMPT)), flush=True)
+            line = run_reference.run(args, config, PROMPT)
+            if "config" in line:
+                line["engine"] = line.pop("config")
+                line["config"] = line_config(config["n_layer"], args.batch)
+            print(json.dumps(line), flush=True)
             return 0
         except Exception as error:      # noqa: BLE001
             why = f"the reference arm failed: {type(error).__name__}: {str(error)[:200]}"
@@ -438,12 +452,10 @@ def main():
         "value": round(args.batch * 1000.0 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "gpt2-xl-shape", "n_layer": XL["n_layer"], "n_layer_run": layers, "n_embd": 1600, "n_head": 25,
-                   "head_dim": 64, "n_inner": 6400, "vocab_size": vocab, "n_positions": 1024, "global_batch": args.batch,
-                   "seq_len": 1024, "prompt_len": PROMPT, "page_size": 16, "weights": "random bf16, cache bf16",
+        "config": line_config(layers, args.batch, not args.no_graph),
+        "engine": {"page_size": 16, "weights": "random bf16", "cache": "bf16", "peaks": peak_source,
                    "context_timed": f"{PROMPT + args.warmup + 1}-{PROMPT + args.warmup + args.steps}",
-                   "parallelism": "single-gpu", "l2": "inputs>L2 (3.1 GB of weights read per step)", "cuda_graph": not args.no_graph,
-                   "activation": "gelu_new", "peaks": peak_source},
+                   "bytes_per_step": int(step_bytes), "path": "Engine.step replayed from a CUDA graph; e2e through the scheduler"},
         "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
