@@ -194,7 +194,7 @@ def test_attention_decode_bf16(K, d, heads, page, n_splits, window):
 
 
 @pytest.mark.parametrize("heads,page", [(5, 16), (25, 16), (17, 32), (3, 64), (2, 128), (33, 16)])
-@pytest.mark.parametrize("n_splits", [1, 3, 11])
+@pytest.mark.parametrize("n_splits", [1, 2, 3, 8, 11])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode_pages(K, heads, page, n_splits, window):
     """The page-streaming decode kernel (TMA boxes of a group of heads): contexts from 1 to 1000 keys that end anywhere
