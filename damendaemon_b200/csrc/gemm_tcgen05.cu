@@ -94,6 +94,10 @@ template <int BN> struct ClusterConfig {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + REDUCE_BYTES + BIAS_BYTES;
 };
 
+// Which 16-byte piece of its row (BN floats) feature lf's piece c is stored at: c ^ reduce_swizzle(lf). Rows of 64
+// bytes (16 tokens) come two to a 128-byte line, so the feature's bit 0 already separates them.
+template <int BN> __device__ __forceinline__ int reduce_swizzle(int lf) { return BN >= 32 ? (lf & 7) : ((lf >> 1) & 3); }
+
 // Ask L2 to fetch this block's share of p.prefetch (16-byte granules, 32 KB per request).
 __device__ __forceinline__ void prefetch_share(const GemmParams& p) {
     if (!p.prefetch_bytes) return;
@@ -831,8 +835,9 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     uint64_t* tmem_full_bar = empty_bar + C::STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // partial tiles sent to this block: [source rank][BN tokens][features of my slice]; neighbouring threads hold
-    // neighbouring features, so both the remote writes and the reads below walk consecutive banks
+    // partial tiles sent to this block: [source rank][feature of my slice][BN tokens], the 16-byte pieces of a
+    // feature's row swizzled by the feature (reduce_swizzle) so that eight neighbouring features' pieces lie in
+    // different banks, for the remote writes as for the reads below
     float* reduce_buf = reinterpret_cast<float*>(tiles + C::STAGES * C::STAGE_BYTES + 256);
 
     dd_launch_dependents();      // the next kernel may begin its own set-up (and ask for its weights) at once
@@ -933,8 +938,9 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         const bool have = n_kblocks > 0 && tc::mbar_wait(tmem_full_bar, 0, abort_flag);
         tc::fence_after_sync();
         const int owner = f / slice, lf = f - owner * slice;
-        // my partial row of feature f goes to the block that owns f
-        const uint32_t remote = tc::map_to_rank(reduce_buf + (size_t)rank * BN * slice + lf, (uint32_t)owner);
+        // my partial row of feature f (BN tokens) goes to the block that owns f, 16 bytes a store
+        const uint32_t remote = tc::map_to_rank(reduce_buf + ((size_t)rank * slice + lf) * BN, (uint32_t)owner);
+        const int sw = reduce_swizzle<BN>(lf);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -945,7 +951,9 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 for (int j = 0; j < 16; ++j) r[j] = 0;    // a block without k-blocks (or one that gave up) adds zeros
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) tc::st_cluster_f32(remote + (uint32_t)((c0 + j) * slice) * 4, __uint_as_float(r[j]));
+            for (int q = 0; q < 4; ++q)
+                if (m0 + c0 + 4 * q < p.M)                // pieces beyond the last token are never read
+                    tc::st_cluster_f32x4(remote + (uint32_t)(((c0 / 4 + q) ^ sw) * 16), r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
         }
     }
     __syncwarp();
@@ -957,32 +965,32 @@ gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         const int tid = threadIdx.x - 64;                 // 0..127
         const int first_feature = rank * slice;
         const int my_features = max(0, min(slice, BM - first_feature));
-        // Eight outputs of a thread at a time: their residual values (the output itself, as a rule, so no load may be
-        // moved across a store by the compiler) are all requested before the first result is written; one after the
-        // other, each cost a trip to L2.
-        const int total = my_features * BN;
-        for (int base = tid; base < total; base += 128 * 8) {
-            float res[8];
+        // A thread finishes four consecutive tokens of one feature at a time (neighbouring threads, neighbouring
+        // features): their residual values (the output itself, as a rule, so no load may be moved across a store by
+        // the compiler) are requested before the partial rows are summed; one after the other, each cost a trip to L2.
+        constexpr int CHUNKS = BN / 4;
+        const int items = my_features * min(CHUNKS, (p.M - m0 + 3) / 4);      // only pieces that hold a token
+        for (int item = tid; item < items; item += 128) {
+            const int lf = item % my_features, c = item / my_features;
+            const int n = n0 + first_feature + lf, m = m0 + 4 * c;
+            float res[4];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int idx = base + u * 128;
-                const int lf = idx % my_features, tok = idx / my_features;   // neighbouring threads, neighbouring features
-                const int n = n0 + first_feature + lf, m = m0 + tok;
-                res[u] = (p.residual && idx < total && n < p.N && m < p.M) ? p.residual[(size_t)m * p.ldr + n] : 0.f;
+            for (int j = 0; j < 4; ++j)
+                res[j] = (p.residual && n < p.N && m + j < p.M) ? p.residual[(size_t)(m + j) * p.ldr + n] : 0.f;
+            const float* mine = reduce_buf + (size_t)lf * BN + 4 * (c ^ reduce_swizzle<BN>(lf));
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < S; ++r) {
+                const float4 a = *reinterpret_cast<const float4*>(mine + (size_t)r * slice * BN);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
             }
+            if (n >= p.N) continue;
+            const float u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int idx = base + u * 128;
-                if (idx >= total) break;
-                const int lf = idx % my_features, tok = idx / my_features;
-                const int n = n0 + first_feature + lf, m = m0 + tok;
-                if (n >= p.N || m >= p.M) continue;
-                float v = 0.f;
-                for (int r = 0; r < S; ++r) v += reduce_buf[((size_t)r * BN + tok) * slice + lf];
-                v += bias_s[lf];
-                v = activation_for(v, p.act, p.out_dtype) + res[u];
-                if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-                else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+            for (int j = 0; j < 4; ++j) {
+                if (m + j >= p.M) break;
+                const float y = activation_for(u[j] + bias_s[lf], p.act, p.out_dtype) + res[j];
+                if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)(m + j) * p.ldo + n] = __float2bfloat16_rn(y);
+                else reinterpret_cast<float*>(p.out)[(size_t)(m + j) * p.ldo + n] = y;
             }
         }
     }

@@ -195,6 +195,10 @@ __device__ __forceinline__ uint32_t map_to_rank(const void* local, uint32_t rank
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// four values with one instruction (addr 16-byte aligned)
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
 // ---- two SMs on one tile (cta_group::2): the blocks of a cluster of two; rank 0 issues the MMAs ----
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t columns) {
