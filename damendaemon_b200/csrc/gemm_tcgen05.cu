@@ -1063,6 +1063,8 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParam
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+        e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: clusters of more than 8 blocks refused: %s", cudaGetErrorString(e));
         configured = true;
     }
     const int tiles = dd_ceil_div(p.N, BM) * dd_ceil_div(p.M, BN);
@@ -1166,8 +1168,27 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
         if (cluster) *cluster = pair ? 2 : 0;
         return 1;
     }
+    // 17 to 64 tokens and a short K: tiles of 16 tokens in clusters, if about 1.35 blocks per SM (and no more than 1.45)
+    // leave every tile at least two splits. Measured at 32 tokens: 1600 x 1600 takes 4.7 us in 26 tiles x 5 splits
+    // against 7.1 us unsplit in tiles of 32 tokens, 6400 x 1600 7.8 against 8.4 us; with more blocks than that the
+    // clusters come in two waves (4800 x 1600 at 48 tokens: 8.0 us in 114 tiles x 2 against 7.6 us unsplit).
+    int mid_splits = 0;
+    if (M > 16 && !long_k && cluster) {
+        const int t16 = dd_ceil_div(N, BM) * dd_ceil_div(M, 16);
+        int s = (sm_count * 27 / 20 + t16 / 2) / t16;
+        while (s >= 2 && t16 * s > sm_count * 29 / 20) --s;
+        if (s > kblocks / 2) s = kblocks / 2;
+        if (s >= 2) {
+            mid_splits = s;
+            bn = 16;
+        }
+    }
     if (token_tile) *token_tile = bn;
     if (cluster) *cluster = 0;
+    if (mid_splits) {
+        *cluster = 1;
+        return mid_splits;
+    }
     const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, bn);
     // A step of a few tokens has a few dozen tiles at most: split K inside clusters so that about as many
     // blocks as there are SMs stream the weights, all in one wave (a cluster must be resident as a whole).
@@ -1180,7 +1201,11 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
         // their weights beside this one's: about 1.35 blocks per SM measured best (4800 features: 5 or 6 splits 6.3 us,
         // 3 splits 7.0; 6400 features: 4 splits 6.8, 2 splits 8.5; more than two blocks per SM: 10.7 and more).
         splits = bn == 16 ? (sm_count * 27 / 20 + tiles / 2) / tiles : sm_count / tiles;
-        if (splits > 8) splits = 8;
+        // clusters of up to 16 blocks exist, but beyond 8 the wider tiles lose (6400 -> 1600 at 32 tokens: 7.2 us in 8
+        // splits, 12.7 in 10), and the tiles of 16 tokens gain little beyond 12 (1600 x 1600 at 8 tokens: 4.25 us in 7
+        // splits, 4.1 in 9; 6400 -> 1600: 7.0 in 8, 6.8 in 10 to 12, 7.1 in 16)
+        const int most = bn == 16 ? 12 : 8;
+        if (splits > most) splits = most;
         if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
         if (splits > 1 && cluster) *cluster = 1;
@@ -1191,7 +1216,7 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
 // X [M,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw); bias [N] f32 or null; residual [M,N] f32
 // (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). token_tile 16/32/64: tiles
 // of 128 features x token_tile tokens; 128/192/256: tiles of 128 tokens x token_tile features, no K split.
-// cluster = 1: splits (at most 8) are the blocks of a cluster and reduce over distributed shared memory
+// cluster = 1: splits (at most 16) are the blocks of a cluster and reduce over distributed shared memory
 // (token_tile <= 64); cluster = 2: two SMs per tile of 256 tokens x token_tile features (tcgen05
 // cta_group::2), token_tile 128/192/256; cluster = 0 with splits > 1 (token_tile <= 64): workspace f32
 // [splits*M*N] and counters int32 [tiles], zero before the first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
@@ -1207,8 +1232,8 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     if (out_dtype != DD_BF16 && out_dtype != DD_F32) return dd_fail("dd_gemm_tcgen05: unknown output dtype %d", out_dtype);
     const int kblocks = dd_ceil_div(K, BK);
     if (splits < 1 || splits > kblocks) return dd_fail("dd_gemm_tcgen05: bad split count %d for %d k-blocks", splits, kblocks);
-    if (cluster == 1 && (splits > 8 || token_tile > 64))
-        return dd_fail("dd_gemm_tcgen05: a cluster has at most 8 blocks and a token tile of at most 64 (got %d, %d)", splits, token_tile);
+    if (cluster == 1 && (splits > 16 || token_tile > 64))
+        return dd_fail("dd_gemm_tcgen05: a cluster has at most 16 blocks and a token tile of at most 64 (got %d, %d)", splits, token_tile);
     if (cluster == 2 && (splits != 1 || (token_tile != 128 && token_tile != 192 && token_tile != 256)))
         return dd_fail("dd_gemm_tcgen05: two SMs per tile take no K split and a token tile of 128, 192 or 256 (got %d, %d)", splits, token_tile);
     GemmParams p;
