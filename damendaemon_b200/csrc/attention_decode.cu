@@ -103,7 +103,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     per = (per + TILE - 1) / TILE * TILE;
     const int k0 = lo + split * per;
     const int k1 = min(hi, k0 + per);
-    const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
+    const int* bt = block_table + (size_t)(tok_entry ? tok_entry[t] : t) * max_blocks;     // no tok_entry: token t is entry t
     for (int blk = k0 / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
         asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + min(blk, max_blocks - 1)));
     const size_t head_plane = (size_t)P * D;

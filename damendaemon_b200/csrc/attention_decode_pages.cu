@@ -87,7 +87,8 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
     const int per = (last_page - first_page + n_splits) / n_splits;      // pages per split, rounded up
     const int page0 = first_page + split * per;
     const int n_mine = max(0, min(last_page + 1, page0 + per) - page0);
-    const int* bt = p.block_table + (size_t)p.tok_entry[t] * p.max_blocks;
+    // without tok_entry token t is entry t (a step of single tokens in entry order): one trip to L2 less before the pages
+    const int* bt = p.block_table + (size_t)(p.tok_entry ? p.tok_entry[t] : t) * p.max_blocks;
     for (int i = threadIdx.x; i < n_mine; i += THREADS) {
         const int blk = page0 + i;
         int page = blk < p.max_blocks ? bt[blk] : -1;

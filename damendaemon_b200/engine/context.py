@@ -21,7 +21,7 @@ class StepContext:
     entry_pos0: object         # int32 [E]   tokens the request held before this step
     block_tables: dict         # cache group name -> int32 [E, max_blocks]
     host: dict = field(default_factory=dict)   # the same lists on the host, for parts that plan there
-    decode_only: bool = False
+    decode_only: bool = False  # every entry brings exactly one token: token t belongs to entry t
     split_context: int = 0     # context length the key splits are planned for
     aligned_starts: bool = False   # every entry starts at a multiple of the model's portion multiple (the key block of
                                    # its prompt attention kernel), so no key block mixes cached and new keys

@@ -395,7 +395,8 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
     """Decode attention (one query per token) over a bfloat16 cache. kernel 'rows': a warp copies key rows 16 bytes
     at a time (see attention_decode_supported); 'pages': whole pages of a group of heads by TMA (see
     attention_decode_pages_supported). With k_new/v_new (row views of the buffer q lives in) the step's own keys and
-    values are used from there and written into the cache by this kernel; otherwise they must be in the cache already."""
+    values are used from there and written into the cache by this kernel; otherwise they must be in the cache already.
+    token_entry None: token t belongs to entry t (a step of single tokens in entry order)."""
     if kernel not in ("rows", "pages"):
         raise KernelError(f"attention_decode: unknown kernel {kernel!r}")
     n_pages, _, kv_heads, page_size, head_dim = cache.shape

@@ -52,12 +52,13 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None):
         # whole pages of a group of heads by TMA; it takes the new keys and values from the projection and writes them
         splits = kernels.attention_decode_pages_splits(ctx.n_tokens, n_heads, page_size, ctx.split_context, q.device)
         splits = max(splits, -(-table.shape[1] // tune.pages_per_block))
-        return kernels.attention_decode(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
+        # (decode only: token t is entry t, so the kernels are spared the look-up)
+        return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
                                         n_splits=splits, k_new=k_new, v_new=v_new, kernel="pages")
     if ctx.decode_only and fast and kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
         # the decode kernel takes the new keys and values from the projection and writes them itself
         splits = ctx.key_splits(n_heads, keys_per_block=tune.row_keys_per_block, blocks_per_sm=tune.row_blocks_per_sm)
-        return kernels.attention_decode(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
+        return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
                                         n_splits=splits, k_new=k_new, v_new=v_new)
     tcgen05 = not ctx.decode_only and tensor and \
         kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, q.dtype)
