@@ -82,10 +82,12 @@ __device__ __forceinline__ float activation_for(float u, int act, int out_dtype)
 }
 
 // The cluster variant keeps a reduce buffer of (BM + 8) x BN floats beside the stages.
-template <int BN> struct ClusterConfig {
+template <int BN, bool DEEP = false> struct ClusterConfig {
     // 16 tokens: 5 stages, so that two blocks fit on an SM, with enough splits that a block seldom reuses a stage
     // (with the splits of the 8-stage rings, 5 stages measured 15-40% slower; with more splits, 5-20% faster)
-    static constexpr int STAGES = BN >= 64 ? 6 : (BN == 16 ? 5 : 8);
+    // DEEP (16 tokens only): 10 stages, one block per SM, for a long K: a block's whole share of the weights is
+    // asked for before the activations exist
+    static constexpr int STAGES = DEEP ? 10 : (BN >= 64 ? 6 : (BN == 16 ? 5 : 8));
     static constexpr int STAGE_BYTES = Config<BN>::STAGE_BYTES;
     static constexpr int A_BYTES = Config<BN>::A_BYTES;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -823,11 +825,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 // feature, its partial row of BN tokens into the owner's shared memory (st.shared::cluster), one
 // cluster barrier later the owner adds the S partials in rank order (deterministic) and applies the
 // epilogue. No global workspace, no counters, no second pass through L2.
-template <int BN>
+template <int BN, bool DEEP>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                             const GemmParams p) {
-    using C = ClusterConfig<BN>;
+    using C = ClusterConfig<BN, DEEP>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
@@ -1056,14 +1058,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cu
     return dd_check_launch("dd_gemm_tcgen05");
 }
 
-template <int BN>
+template <int BN, bool DEEP = false>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t s) {
-    using C = ClusterConfig<BN>;
+    using C = ClusterConfig<BN, DEEP>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: shared memory of %d bytes refused: %s", C::SMEM_BYTES, cudaGetErrorString(e));
-        e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        e = cudaFuncSetAttribute(gemm_tcgen05_cluster_kernel<BN, DEEP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05: clusters of more than 8 blocks refused: %s", cudaGetErrorString(e));
         configured = true;
     }
@@ -1082,7 +1084,7 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParam
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attrs;
     config.numAttrs = dd_pdl_enabled ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_cluster_kernel<BN>, mw, mx, p);
+    cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_cluster_kernel<BN, DEEP>, mw, mx, p);
     if (e != cudaSuccess) return dd_fail("dd_gemm_tcgen05 (cluster of %d): %s", p.splits, cudaGetErrorString(e));
     return dd_check_launch("dd_gemm_tcgen05");
 }
@@ -1206,6 +1208,16 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
         // splits, 4.1 in 9; 6400 -> 1600: 7.0 in 8, 6.8 in 10 to 12, 7.1 in 16)
         const int most = bn == 16 ? 12 : 8;
         if (splits > most) splits = most;
+        if (bn == 16 && cluster && tiles * 8 <= sm_count) {
+            // A narrow product (1600 features: 13 tiles): one block per SM with a ring of 10 stages, clusters of at most 8
+            // (two of them fit a GPC), at least 5 k-blocks a block. Measured at 8 tokens: 1600 x 1600 3.7 us in 5 splits
+            // against 4.1 us in 9 splits of 5-stage rings; 6400 -> 1600 6.6 us in 8 splits against 6.9 us in 12.
+            const int deep = kblocks / 5 < 8 ? kblocks / 5 : 8;
+            if (deep >= 2) {
+                *cluster = 3;
+                return deep;
+            }
+        }
         if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
         if (splits > 1 && cluster) *cluster = 1;
@@ -1217,7 +1229,7 @@ DD_API int dd_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* token_ti
 // (row stride ldr, may alias out) or null; out [M,N] bf16 or f32 (row stride ldo). token_tile 16/32/64: tiles
 // of 128 features x token_tile tokens; 128/192/256: tiles of 128 tokens x token_tile features, no K split.
 // cluster = 1: splits (at most 16) are the blocks of a cluster and reduce over distributed shared memory
-// (token_tile <= 64); cluster = 2: two SMs per tile of 256 tokens x token_tile features (tcgen05
+// (token_tile <= 64); cluster = 3: the same with rings of 10 stages and one block per SM (token_tile 16); cluster = 2: two SMs per tile of 256 tokens x token_tile features (tcgen05
 // cta_group::2), token_tile 128/192/256; cluster = 0 with splits > 1 (token_tile <= 64): workspace f32
 // [splits*M*N] and counters int32 [tiles], zero before the first launch. prefetch/prefetch_bytes: null/0, or memory that a later kernel streams once (the next
 // weight matrix of a decode step): this kernel's blocks ask L2 to fetch it while they run.
@@ -1232,7 +1244,8 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     if (out_dtype != DD_BF16 && out_dtype != DD_F32) return dd_fail("dd_gemm_tcgen05: unknown output dtype %d", out_dtype);
     const int kblocks = dd_ceil_div(K, BK);
     if (splits < 1 || splits > kblocks) return dd_fail("dd_gemm_tcgen05: bad split count %d for %d k-blocks", splits, kblocks);
-    if (cluster == 1 && (splits > 16 || token_tile > 64))
+    if (cluster == 3 && token_tile != 16) return dd_fail("dd_gemm_tcgen05: the deep rings are for token tiles of 16 (got %d)", token_tile);
+    if ((cluster == 1 || cluster == 3) && (splits > 16 || token_tile > 64))
         return dd_fail("dd_gemm_tcgen05: a cluster has at most 16 blocks and a token tile of at most 64 (got %d, %d)", splits, token_tile);
     if (cluster == 2 && (splits != 1 || (token_tile != 128 && token_tile != 192 && token_tile != 256)))
         return dd_fail("dd_gemm_tcgen05: two SMs per tile take no K split and a token tile of 128, 192 or 256 (got %d, %d)", splits, token_tile);
@@ -1243,7 +1256,7 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
     p.prefetch_bytes = (prefetch && prefetch_bytes > 0 && !((uintptr_t)prefetch & 15)) ? (unsigned long long)prefetch_bytes : 0;
     p.splits = splits; p.kblocks_per_split = dd_ceil_div(kblocks, splits);
     p.splits = dd_ceil_div(kblocks, p.kblocks_per_split);     // no empty split
-    if (p.splits == 1 && cluster == 1) cluster = 0;
+    if (p.splits == 1 && (cluster == 1 || cluster == 3)) cluster = 0;
     if (p.splits > 1 && !cluster) {
         const int tiles = dd_ceil_div(N, BM) * dd_ceil_div(M, token_tile);
         if (!workspace || !counters || n_counters < tiles)
@@ -1269,6 +1282,7 @@ DD_API int dd_gemm_tcgen05(const void* X, int ldx, const void* W, int ldw, const
             case 256: return launch_pair<256>(mw, mx, p, s);
         }
     }
+    if (cluster == 3) return launch_cluster<16, true>(mw, mx, p, s);
     if (cluster) {
         switch (token_tile) {
             case 16: return launch_cluster<16>(mw, mx, p, s);

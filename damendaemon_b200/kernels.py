@@ -338,8 +338,9 @@ def gemm_tcgen05(a, w, bias=None, residual=None, activation=None, out_dtype=None
                  cluster=None, prefetch=None):
     """act(a @ w.T + bias) (+ residual) on the tcgen05 tensor cores. a [M,K] and w [N,K] bfloat16,
     bias/residual float32, out bfloat16 or float32. K and the row strides must be multiples of 8.
-    splits/token_tile/cluster override the kernel's own plan (cluster: reduce the K splits inside a
-    thread-block cluster instead of through a workspace). prefetch: a tensor that a later kernel will
+    splits/token_tile/cluster override the kernel's own plan (cluster 1: reduce the K splits inside a
+    thread-block cluster instead of through a workspace; 3: the same with rings of 10 stages, one block per SM,
+    token tiles of 16 only; 2: two SMs on a tile of 256 tokens). prefetch: a tensor that a later kernel will
     stream (the next weight matrix of a decode step); this kernel asks L2 to fetch it meanwhile."""
     _rows(a, "a"), _rows(w, "w")
     M, K = a.shape

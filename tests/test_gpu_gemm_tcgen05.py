@@ -68,21 +68,24 @@ def test_forced_splits_and_tiles(K, splits, tile):
     assert torch.equal(out, again), "split-K sums in a fixed order: two runs are bit-equal"
 
 
-@pytest.mark.parametrize("splits", [2, 3, 5, 8])
-@pytest.mark.parametrize("tokens,tile", [(1, 16), (8, 16), (13, 16), (30, 32), (64, 64)])
-def test_cluster_split(K, splits, tokens, tile):
-    """K split inside a thread-block cluster, partial tiles reduced over distributed shared memory."""
+@pytest.mark.parametrize("splits", [2, 3, 5, 8, 12, 16])
+@pytest.mark.parametrize("tokens,tile,cluster", [(1, 16, 1), (8, 16, 1), (13, 16, 1), (30, 32, 1), (64, 64, 1), (40, 16, 1),
+                                                 (64, 16, 1), (50, 32, 1), (1, 16, 3), (6, 16, 3), (16, 16, 3), (35, 16, 3)])
+def test_cluster_split(K, splits, tokens, tile, cluster):
+    """K split inside a thread-block cluster of up to 16 blocks, partial tiles reduced over distributed shared memory
+    (16 bytes a store, only the pieces that hold a token); cluster 3: the rings of 10 stages (with 2 splits a block
+    has more k-blocks than stages). Token counts that end anywhere in a piece of four and in a tile."""
     a, w, bias, res = operands(tokens, 700, 1600, seed=4)
     ref = a.double() @ w.double().t() + bias.double()
-    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=1)
-    again = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=1)
+    out = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=cluster)
+    again = K.gemm_tcgen05(a, w, bias, out_dtype=torch.float32, splits=splits, token_tile=tile, cluster=cluster)
     assert K.read_error_flag(DEV) == 0
     assert (out.double() - ref).abs().max() < 1e-3
     assert torch.equal(out, again), "the partial tiles are added in rank order: two runs are bit-equal"
     stream = res.clone()
-    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream, splits=splits, token_tile=tile, cluster=1)
+    K.gemm_tcgen05(a, w, bias, residual=stream, out_dtype=torch.float32, out=stream, splits=splits, token_tile=tile, cluster=cluster)
     assert (stream.double() - (ref + res.double())).abs().max() < 1e-3
-    gelu = K.gemm_tcgen05(a, w, bias, activation="gelu_new", splits=splits, token_tile=tile, cluster=1)
+    gelu = K.gemm_tcgen05(a, w, bias, activation="gelu_new", splits=splits, token_tile=tile, cluster=cluster)
     u = ref
     want = 0.5 * u * (1 + torch.tanh(math.sqrt(2 / math.pi) * (u + 0.044715 * u ** 3)))
     assert (gelu.double() - want).abs().max() < 2.0 ** -8 * float(want.abs().max()) + 1e-3
