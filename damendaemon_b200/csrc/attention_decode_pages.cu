@@ -21,7 +21,7 @@
 
 namespace {
 constexpr int D = 64, TILE = 16, WARPS = 8, THREADS = WARPS * 32, HEADS_PER_WARP = 1, MAX_GROUP = WARPS * HEADS_PER_WARP;
-constexpr int MAX_BLOCK_PAGES = 128;          // pages a block may own (their ids live in shared memory)
+constexpr int MAX_BLOCK_PAGES = 128;          // pages a block may own (their ids live in shared memory); 1 << 7 below
 constexpr int MAX_STAGES = 6;
 
 struct Params {
@@ -38,6 +38,9 @@ struct Params {
     int* counters;
     int* error_flag;
     int q_stride, out_stride, max_blocks, H, G, P, n_pages, window, stages;
+    int n_tokens, log2_P;
+    int deal;                    // 1: more blocks in the grid than can be resident, so the splits are dealt out (see the kernel)
+    float inv_block_budget;      // 1 / blocks that can be resident at once: the key splits are dealt out against them
     float scale_log2e;
 };
 
@@ -78,13 +81,48 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
 
     // Positions, entries and the block table are this step's inputs, not an earlier kernel's results: they are read
     // while the kernel before this one is still running.
-    const int split = blockIdx.x, n_splits = gridDim.x, g = blockIdx.y, t = blockIdx.z;
+    // The grid holds the most splits a token may need (gridDim.z, the slowest index, so that the splits every token
+    // has are launched first); how many a token gets is decided here, from all tokens' positions, so that blocks do
+    // about equal work whatever the contexts are: the step's pages x head groups are dealt out over the blocks that
+    // can be resident at once, a token takes its share rounded to the nearest count, and the blocks beyond it leave.
+    // (One split per token with contexts spread over 1..1000 made the kernel as long as its longest token: 61 us for
+    // 64 tokens x 20 heads against 44 us with the long ones cut in three; with equal contexts nothing changes.)
+    const int split = blockIdx.z, g = blockIdx.y, t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane >> 2, t4 = lane & 3;
+    // (page sizes are powers of two, and the block budget's reciprocal comes from the host: a chain of integer
+    // divisions here, a hundred cycles each, stood between the positions and the first page request)
+    const int span = p.max_blocks << p.log2_P;              // positions the block table can describe
+    auto pages_of = [&](int position, int* first) {
+        position = min(max(position, 0), span - 1);
+        const int from = p.window > 0 ? max(0, position - p.window + 1) : 0;
+        if (first) *first = from >> p.log2_P;
+        return (position >> p.log2_P) - (from >> p.log2_P) + 1;
+    };
+    // every warp adds up the pages of all tokens for itself (a load per lane and five shuffles for up to 32 tokens):
+    // no barrier and no shared memory stand between the positions and the first page request
     const int pos = p.tok_pos[t];
+    int total_pages = 0;
+    if (p.deal) {
+        for (int i = lane; i < p.n_tokens; i += 32) total_pages += pages_of(p.tok_pos[i], nullptr);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total_pages += __shfl_xor_sync(0xffffffffu, total_pages, o);
+    }
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int first_page = lo / p.P, last_page = pos / p.P;
-    const int per = (last_page - first_page + n_splits) / n_splits;      // pages per split, rounded up
+    int first_page = 0;
+    const int my_pages = pages_of(pos, &first_page);
+    const int last_page = first_page + my_pages - 1;
+    // pages a block should take: all pages x groups over the blocks that can be resident (every block of a token does
+    // the same arithmetic on the same numbers, so they agree whatever the rounding)
+    int n_splits = gridDim.z;               // few tokens: every token may have all the splits, the blocks fit anyway
+    if (p.deal) {
+        const float share = fmaxf(1.f, ceilf((float)total_pages * (float)gridDim.y * p.inv_block_budget));
+        n_splits = max(1, (int)(((float)my_pages + 0.5f * share) / share));
+        n_splits = max(n_splits, (my_pages + MAX_BLOCK_PAGES - 1) >> 7);
+        n_splits = min(n_splits, (int)gridDim.z);
+        if (split >= n_splits) return;
+    }
+    const int per = (my_pages + n_splits - 1) / n_splits;                // pages per split, rounded up
     const int page0 = first_page + split * per;
     const int n_mine = max(0, min(last_page + 1, page0 + per) - page0);
     // without tok_entry token t is entry t (a step of single tokens in entry order): one trip to L2 less before the pages
@@ -250,7 +288,7 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) *reinterpret_cast<uint32_t*>(dst + j * 8) = pack_bf16(o[u][j][0] * inv, o[u][j][1] * inv);
         } else {
-            const size_t item = ((size_t)t * p.H + h) * n_splits + split;
+            const size_t item = ((size_t)t * p.H + h) * gridDim.z + split;     // the scratch is laid out for the most splits
             float* dst = p.part_o + item * D + 2 * t4;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[u][j][0], o[u][j][1]);
@@ -272,7 +310,7 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
     // and outputs of eight splits requested together and merged with a running maximum.
     for (int idx = threadIdx.x; idx < group_heads * D; idx += THREADS) {
         const int h = head0 + idx / D, d = idx % D;
-        const size_t first = ((size_t)t * p.H + h) * n_splits;
+        const size_t first = ((size_t)t * p.H + h) * gridDim.z;
         float Mx = -CUDART_INF_F, Lx = 0.f, acc = 0.f;
         for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
             float mm[8], ll[8], oo[8];
@@ -336,15 +374,19 @@ DD_API int dd_attention_decode_pages_supported(int n_heads, int n_kv_heads, int 
            (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
 }
 
-// How many key splits dd_attention_decode_pages should be given for n_tokens tokens whose longest context is
-// `context` keys.
+// The most key splits a token of dd_attention_decode_pages may need when the longest context is `context` keys (the
+// kernel's n_splits argument: the grid is laid out for it; how many splits each token really gets the kernel decides
+// from all tokens' positions). At most eight, which merge in one trip to L2 (measured at 8 tokens x 25 heads x 768
+// keys: 8 splits, all blocks resident, 13 us; a second wave of blocks 18 us).
 DD_API int dd_attention_decode_pages_splits(int n_tokens, int n_heads, int page_size, int context, int sm_count) {
     int group = 0, n_groups = 0;
     grouping(n_heads, page_size, &group, &n_groups);
     const int pages = dd_ceil_div(context < 1 ? 1 : context, page_size);
-    // all blocks resident at once (two per SM), and at most eight splits, which merge in one trip to L2: measured at 8
-    // tokens x 25 heads x 768 keys, 8 splits take 13 us, 10 splits (a second wave of blocks) 18 us
-    int splits = (2 * sm_count) / (n_tokens * n_groups);
+    // A token gets pages / (all pages x groups / resident blocks) splits: with equal contexts that is resident blocks
+    // / (tokens x groups); a token 2.5 times as long as the average gets 2.5 times as many, and the grid allows for
+    // that much. More would only add blocks that leave at once, and while those wait for a place the next kernel
+    // cannot start its prologue (64 tokens, 8 splits allowed, 1 taken: 58 us against 56).
+    int splits = dd_ceil_div(5ll * 2 * sm_count, 2ll * (n_tokens < 1 ? 1 : n_tokens) * n_groups);
     if (splits > 8) splits = 8;
     if (splits > pages) splits = pages;
     if (splits < dd_ceil_div(pages, MAX_BLOCK_PAGES)) splits = dd_ceil_div(pages, MAX_BLOCK_PAGES);
@@ -377,7 +419,21 @@ DD_API int dd_attention_decode_pages(const void* q, int q_stride, const void* k_
     grouping(n_heads, page_size, &p.G, &n_groups);
     const int box_rows = p.G * page_size, box_bytes = box_rows * 128;
     p.stages = (106 * 1024) / (2 * box_bytes);            // two blocks per SM
-    if (p.stages < 2) p.stages = (210 * 1024) / (2 * box_bytes);      // large pages: one block per SM
+    int blocks_per_sm = 2;
+    if (p.stages < 2) {                                               // large pages: one block per SM
+        p.stages = (210 * 1024) / (2 * box_bytes);
+        blocks_per_sm = 1;
+    }
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    p.inv_block_budget = 1.0f / (float)(blocks_per_sm * sm_count);
+    p.deal = (long long)n_tokens * n_groups * n_splits > (long long)blocks_per_sm * sm_count;
+    p.log2_P = page_size == 16 ? 4 : (page_size == 32 ? 5 : (page_size == 64 ? 6 : 7));
     if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
     if (p.stages < 2) return dd_fail("dd_attention_decode_pages: a page of %d heads x %d tokens does not fit twice into shared memory", p.G, page_size);
     const int smem = p.stages * 2 * box_bytes + 1024 + MAX_STAGES * 8 + MAX_BLOCK_PAGES * 4;
@@ -400,6 +456,7 @@ DD_API int dd_attention_decode_pages(const void* q, int q_stride, const void* k_
     p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml; p.counters = counters; p.error_flag = error_flag;
     p.q_stride = q_stride; p.out_stride = out_stride; p.max_blocks = max_blocks; p.H = n_heads; p.P = page_size;
     p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
-    dd_launch(attention_decode_pages_kernel, dim3(n_splits, n_groups, n_tokens), dim3(THREADS), (size_t)smem, (cudaStream_t)stream, map, p);
+    p.n_tokens = n_tokens;
+    dd_launch(attention_decode_pages_kernel, dim3(n_tokens, n_groups, n_splits), dim3(THREADS), (size_t)smem, (cudaStream_t)stream, map, p);
     return dd_check_launch("dd_attention_decode_pages");
 }

@@ -23,19 +23,25 @@ class StepContext:
     host: dict = field(default_factory=dict)   # the same lists on the host, for parts that plan there
     decode_only: bool = False  # every entry brings exactly one token: token t belongs to entry t
     split_context: int = 0     # context length the key splits are planned for
-    aligned_starts: bool = False   # every entry starts at a multiple of the model's portion multiple (the key block of
-                                   # its prompt attention kernel), so no key block mixes cached and new keys
+    n_single: int = 0          # the first n_single entries bring exactly one token each (token t is entry t there);
+                               # the engine lays single-token entries out first
+    aligned_starts: bool = False   # every entry after the first n_single starts at a multiple of the model's portion
+                                   # multiple (the key block of its prompt attention kernel), so no key block of theirs
+                                   # mixes cached and new keys
     runtime: object = None
     sm_count: int = 148
 
     def block_table(self, group):
         return self.block_tables[group.name]
 
-    def key_splits(self, n_heads, keys_per_block=64, blocks_per_sm=16):
-        """How many pieces each row's keys are cut into so that a decode-only step fills the GPU."""
-        if not self.decode_only:
-            return 1
-        want = -(-(self.sm_count * blocks_per_sm) // max(1, self.n_tokens * n_heads))
+    def key_splits(self, n_heads, keys_per_block=64, blocks_per_sm=16, n_tokens=None):
+        """How many pieces each row's keys are cut into so that a decode-only step (or, with n_tokens given, the
+        single tokens of a mixed step) fills the GPU."""
+        if n_tokens is None:
+            if not self.decode_only:
+                return 1
+            n_tokens = self.n_tokens
+        want = -(-(self.sm_count * blocks_per_sm) // max(1, n_tokens * n_heads))
         return max(1, min(want, (self.split_context + keys_per_block - 1) // keys_per_block, 32))
 
     def attend(self, q, k, v, cache, n_heads, scale, window=None):

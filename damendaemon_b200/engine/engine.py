@@ -210,7 +210,9 @@ class Engine:
         at["total"] = o
         return at
 
-    def _fill(self, entries, lengths, at, arr):
+    def _fill(self, entries, lengths, at, arr, order=None):
+        """Write the step's arrays. order: the entries' indices in the order they are laid out in (None: as given);
+        the wanted rows keep the order of the entries as given. Returns slots and first positions in layout order."""
         N, E = sum(lengths), len(entries)
         MB = self.cache.max_blocks
         ids, pos, ent = (arr[at[k][0]:at[k][1]] for k in ("ids", "pos", "ent"))
@@ -235,27 +237,30 @@ class Engine:
                 a, b = at["table:" + g.name]
                 arr[a:b].reshape(E, MB)[:] = g.table_array[slots]
             return slots, p0s
-        cursor, wi, slots = 0, 0, []
-        for i, e in enumerate(entries):
-            n = lengths[i]
+        cursor, slots, first_row = 0, [], [0] * E
+        for j, i in enumerate(range(E) if order is None else order):
+            e, n = entries[i], lengths[i]
             p0 = self.cache.length[e.request]
             ids[cursor:cursor + n] = e.tokens
             pos[cursor:cursor + n] = np.arange(p0, p0 + n, dtype=np.int32)
-            ent[cursor:cursor + n] = i
-            for w in e.want:
-                want[wi] = cursor + w
-                wi += 1
+            ent[cursor:cursor + n] = j
             s = self.cache.slot_of[e.request]
             slots.append(s)
-            slot[i], start[i], pos0[i] = s, cursor, p0
+            slot[j], start[j], pos0[j] = s, cursor, p0
+            first_row[i] = cursor
             cursor += n
         start[E] = cursor
+        wi = 0
+        for i, e in enumerate(entries):
+            for w in e.want:
+                want[wi] = first_row[i] + w
+                wi += 1
         for g in self.cache.groups:
             a, b = at["table:" + g.name]
             arr[a:b].reshape(E, MB)[:] = g.table_array[slots]
         return slots, [int(x) for x in pos0]
 
-    def _context(self, N, E, M, at, decode_only, split_context, host=None, aligned=False):
+    def _context(self, N, E, M, at, decode_only, split_context, host=None, aligned=False, n_single=0):
         dev, MB = self._meta_dev, self.cache.max_blocks
         view = lambda k: dev[at[k][0]:at[k][1]]
         return StepContext(
@@ -264,11 +269,11 @@ class Engine:
             entry_pos0=view("pos0"),
             block_tables={g.name: view("table:" + g.name).view(E, MB) for g in self.cache.groups},
             host=host or {}, decode_only=decode_only, split_context=split_context, runtime=self.runtime,
-            sm_count=self.sm_count, aligned_starts=aligned)
+            sm_count=self.sm_count, aligned_starts=aligned, n_single=n_single)
 
-    def _upload(self, entries, lengths, at):
+    def _upload(self, entries, lengths, at, order=None):
         host = self._meta_buffers(at["total"])
-        slots, pos0 = self._fill(entries, lengths, at, self._meta_numpy[self._turn])
+        slots, pos0 = self._fill(entries, lengths, at, self._meta_numpy[self._turn], order)
         kernels.copy_to_device(self._meta_dev, host, at["total"] * 4)
         self.last_h2d_bytes = at["total"] * 4
         self._meta_events[self._turn].record()
@@ -280,21 +285,33 @@ class Engine:
         N, E, M = sum(lengths), len(entries), sum(len(e.want) for e in entries)
         at = self._layout(N, E, M)
         decode_only = N == E
-        slots, pos0 = self._upload(entries, lengths, at)
+        # Entries of a single token are laid out first (a mixer can then give them to a decode kernel as one run of
+        # rows and the rest to a prompt kernel); the logits keep the order of the entries as given. Token ids that
+        # come from the device are in the given order, so then nothing moves and only the leading singles count.
+        order, n_single = None, E
+        if not decode_only:
+            singles = [i for i, n in enumerate(lengths) if n == 1]
+            n_single = len(singles)
+            if device_ids is not None or singles == list(range(n_single)):
+                n_single = next((i for i, n in enumerate(lengths) if n != 1), E)
+            else:
+                order = singles + [i for i, n in enumerate(lengths) if n != 1]
+                lengths = [lengths[i] for i in order]
+        slots, pos0 = self._upload(entries, [len(e.tokens) for e in entries], at, order)
         if device_ids is not None:
             a, b = at["ids"]
             self._meta_dev[a:b].copy_(device_ids.reshape(-1), non_blocking=True)
-        host = {"lengths": lengths, "pos0": pos0, "slots": slots}
+        host = {"lengths": lengths, "pos0": pos0, "slots": slots}            # in layout order, like the device arrays
         block = self.portion_multiple
-        aligned = not decode_only and block > 1 and all(p % block == 0 for p in pos0)
+        aligned = n_single < E and block > 1 and all(p % block == 0 for p in pos0[n_single:])
         if self.use_graph and M > 0 and N <= self.max_graph_tokens:
             # Every kernel reads lengths, positions and page tables from the metadata buffer, and launch shapes
             # depend only on the counts, so a step of counts seen before can be replayed whatever the lengths are.
-            key = (N, E, M, decode_only, aligned)
+            key = (N, E, M, n_single, aligned)
             graph = self._graphs.get(key)
             if graph is None and self._seen.get(key, 0) >= self.capture_after[decode_only]:
                 # this shape has come back often enough: capture it (its first run was eager and warmed everything up)
-                ctx = self._context(N, E, M, at, decode_only, self.max_context, aligned=aligned)
+                ctx = self._context(N, E, M, at, decode_only, self.max_context, aligned=aligned, n_single=n_single)
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.current_stream().synchronize()
                 with torch.cuda.graph(graph), kernels.stream_scope():
@@ -311,7 +328,7 @@ class Engine:
             self._seen[key] = self._seen.get(key, 0) + 1
             if len(self._seen) > 4096:                   # shapes that never came back
                 self._seen = {k: n for k, n in self._seen.items() if n > 1}
-        ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned)
+        ctx = self._context(N, E, M, at, decode_only, max(p + n for p, n in zip(pos0, lengths)), host, aligned, n_single)
         with kernels.stream_scope():
             return self.model.forward(ctx, self._caches)
 

@@ -130,6 +130,35 @@ def test_long_decoding_and_first_tokens(models, dtype):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_single_tokens_anywhere_among_portions(models, name, dtype):
+    """A step that names portions and single tokens in any order: inside, the engine lays the single tokens out first
+    (a decode kernel takes them, a prompt kernel the portions); the logits come back in the order of the entries as
+    given and of their wanted places. Twice, so that the second step reads what the first one cached."""
+    from damendaemon_b200.engine import StepEntry
+    folder, config, requests, want = models[name, dtype]
+    names = [r for r in requests if len(requests[r]) >= 17][:4]
+    engine = engine_for(folder, dtype, 64 * 16, 16)
+    held = {r: 0 for r in names}
+    plans = [[(names[0], 9, [0, 8]), (names[1], 1, [0]), (names[2], 5, []), (names[3], 1, [0])],
+             [(names[3], 1, [0]), (names[0], 3, [2]), (names[1], 1, []), (names[2], 7, [6, 0, 3])]]
+    for plan in plans:
+        entries, places = [], []
+        for r, n, wanted in plan:
+            entries.append(StepEntry(r, requests[r][held[r]:held[r] + n], wanted))
+            places += [(r, held[r] + w) for w in wanted]
+            held[r] += n
+        rows = engine.step(entries).cpu()
+        assert rows.shape[0] == len(places)
+        for (r, position), row in zip(places, rows):
+            err = (row - want[r][position]).abs().max().item()
+            assert err < TOL[name, dtype], f"request {r} position {position}: {err:.3e}"
+    for r in names:
+        engine.finish(r)
+    engine.cache.check()
+
+
 def test_step_validation_changes_nothing(models):
     from damendaemon_b200.cache import PageCapacityError
     from damendaemon_b200.engine import StepEntry, StepError

@@ -230,6 +230,37 @@ def test_attention_decode_pages(K, heads, page, n_splits, window):
     assert 1 <= K.attention_decode_pages_splits(8, heads, page, 1000, DEV) <= (1000 + page - 1) // page
 
 
+@pytest.mark.parametrize("heads,page", [(25, 16), (8, 64), (20, 32)])
+@pytest.mark.parametrize("n_splits", [3, 8])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_pages_deals_its_splits(K, heads, page, n_splits, window):
+    """More blocks in the grid than can be resident: the kernel deals the key splits out from all tokens' positions,
+    long contexts get several, short ones one, and the blocks beyond a token's count leave. Twenty tokens with
+    contexts from 1 to 1000 keys, without an entry index (token t is entry t), then the fused cache write."""
+    K.library("tensor")
+    lengths = [1000, 3, 17, 640, 1, 255, 256, 257, 511, 90, 1000, 33, 800, 64, 128, 5, 700, 16, 15, 999]
+    c = paged_case(K, torch.bfloat16, heads, heads, 64, page, lengths=lengths, new=[1] * len(lengths),
+                   window=window, n_splits=n_splits, spike=5 if window is None else 250)
+    run = lambda q, cache, **kw: K.attention_decode(q, cache, None, c["pos"], c["table"], heads, c["scale"], window,
+                                                    n_splits=n_splits, kernel="pages", **kw)
+    out = run(c["q"], c["cache"])
+    again = run(c["q"], c["cache"])
+    assert K.read_error_flag(DEV) == 0
+    assert not torch.isnan(out.float()).any(), "a key outside the live range was read"
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol(torch.bfloat16)
+    assert torch.equal(out, again), "the split counters were not left at zero"
+    packed = c["packed"]
+    hd = heads * 64
+    wiped = c["cache"].clone()
+    for e, L in enumerate(lengths):
+        wiped[int(c["table"][e, (L - 1) // page]), :, :, (L - 1) % page] = float("nan")
+    fused = run(packed[:, :hd], wiped, k_new=packed[:, hd:2 * hd], v_new=packed[:, 2 * hd:])
+    assert K.read_error_flag(DEV) == 0
+    assert torch.equal(fused, out)
+    same = (wiped == c["cache"]) | (torch.isnan(wiped.float()) & torch.isnan(c["cache"].float()))
+    assert bool(same.all()), "the fused kernel did not write the new key and value into the cache"
+
+
 @pytest.mark.parametrize("d,heads,kv_heads,page", [(64, 5, 5, 16), (128, 4, 2, 8), (64, 6, 1, 32)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attention_prefill_bf16(K, d, heads, kv_heads, page, window):
