@@ -440,6 +440,12 @@ def main():
         points["prefill_4x4096_frac"] = round(prefill_flops(long_config, layers, 4096, 4) / (long_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)
         del rt
         torch.cuda.empty_cache()
+        # the same decode step in true 32-bit (float32 weights and cache, CUDA-core products): the reference's only mode
+        rt = make_runtime(config, args.batch, dtype="float32")
+        f32_ms, _, _ = decode_device_timed(rt.engine, args.batch, 3, 10, vocab)
+        points[f"decode_b{args.batch}_float32"] = round(args.batch * 1000.0 / f32_ms, 1)
+        del rt
+        torch.cuda.empty_cache()
         if layers == XL["n_layer"]:
             for name in sorted(WORKLOADS):          # the scheduler under mixed loads (generated tokens a second)
                 points[f"workload_{name}"] = run_workload(name)["value"]

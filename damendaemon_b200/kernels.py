@@ -98,6 +98,26 @@ def set_pdl(enabled):
 _pdl = True
 
 
+class pdl_scope:
+    """Kernels launched inside run with programmatic dependent launch on or off; the setting that was in force comes
+    back afterwards. The float32 engine turns it off: its kernels (hundreds of blocks of CUDA-core work, no prologue
+    worth starting early) were measured to run a decode step of 12 GPT-2 XL layers in 2.2 ms without it and in 2.6
+    to 4.3 ms with it, while the bfloat16 kernels gain from it everywhere (1.78 against 2.34 ms for 48 layers)."""
+
+    def __init__(self, enabled):
+        self.enabled = bool(enabled)
+
+    def __enter__(self):
+        self.before = _pdl
+        if self.enabled != self.before:
+            set_pdl(self.enabled)
+
+    def __exit__(self, *exc):
+        if _pdl != self.before:
+            set_pdl(self.before)
+        return False
+
+
 def _call(lib, fn, *args, n_kernels=1):
     global launches
     launches += n_kernels
