@@ -89,7 +89,7 @@ gemm_simt_rows_kernel(const float* __restrict__ A, int lda, const float* __restr
                       TO* C, int ldc, int M, int N, int K, int act) {
     constexpr int PER = MR * RB_N / RB_THREADS;             // rows of A per thread (1 to 8)
     static_assert(PER >= 1 && MR * RB_N % RB_THREADS == 0, "a thread owns whole rows");
-    constexpr int RB_STAGES = MR <= 16 ? 6 : 4;             // 35 to 41 KB of static shared memory
+    constexpr int RB_STAGES = MR <= 16 ? 6 : (MR <= 32 ? 4 : 3);   // at most 41 KB of static shared memory
     __shared__ __align__(16) float Ws[RB_STAGES][RB_N][RB_LD];
     __shared__ __align__(16) float As[RB_STAGES][MR][RB_LD];
     const int n0 = blockIdx.x * RB_N;
@@ -165,6 +165,102 @@ int launch_rows(const void* A, int lda, const void* W, int ldw, const float* bia
     return dd_check_launch("dd_gemm_simt");
 }
 
+// ---- many rows (a prompt portion): float32 operands ----
+// Tiles of 128 x 128 outputs, 256 threads with 8 x 8 outputs each (rows ty + 16 i, features tx + 16 j, so that the
+// 16-byte reads of a warp meet no bank twice), k in chunks of 16 through three cp.async stages. Every output is again
+// one chain of fmaf over ascending k from zero: the same bits as the other two kernels.
+constexpr int BG = 128, BG_K = 16, BG_LD = BG_K + 4, BG_STAGES = 3, BG_THREADS = 256;
+constexpr int BG_SMEM = BG_STAGES * 2 * BG * BG_LD * 4;
+
+__global__ void __launch_bounds__(BG_THREADS)
+gemm_simt_big_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
+                     const float* __restrict__ bias, const float* residual, int ldr,
+                     float* C, int ldc, int M, int N, int K, int act) {
+    extern __shared__ __align__(16) float big_smem[];
+    float (*As)[BG][BG_LD] = reinterpret_cast<float (*)[BG][BG_LD]>(big_smem);
+    float (*Ws)[BG][BG_LD] = reinterpret_cast<float (*)[BG][BG_LD]>(big_smem + BG_STAGES * BG * BG_LD);
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * BG, n0 = blockIdx.x * BG;
+    const int chunks = (K + BG_K - 1) / BG_K;
+    // a chunk: 128 rows x 4 pieces of 16 bytes for each operand, two pieces of each per thread
+    auto load = [&](int c) {
+        const int st = c % BG_STAGES, k0 = c * BG_K;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int piece = threadIdx.x + i * BG_THREADS, row = piece >> 2, kk = (piece & 3) * 4;
+            const bool in_k = k0 + kk < K;
+            const bool a_live = in_k && m0 + row < M, w_live = in_k && n0 + row < N;
+            cp_async16(&As[st][row][kk], A + (size_t)(a_live ? m0 + row : 0) * lda + (a_live ? k0 + kk : 0), a_live);
+            cp_async16(&Ws[st][row][kk], W + (size_t)(w_live ? n0 + row : 0) * ldw + (w_live ? k0 + kk : 0), w_live);
+        }
+    };
+    for (int c = 0; c < BG_STAGES - 1; ++c) {
+        if (c < chunks) load(c);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    for (int c = 0; c < chunks; ++c) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(BG_STAGES - 2) : "memory");
+        __syncthreads();
+        if (c + BG_STAGES - 1 < chunks) load(c + BG_STAGES - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = c % BG_STAGES;
+#pragma unroll
+        for (int k4 = 0; k4 < BG_K; k4 += 4) {
+            float4 a[8], w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(&As[st][ty + 16 * i][k4]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = *reinterpret_cast<const float4*>(&Ws[st][tx + 16 * j][k4]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[i][j] = fmaf(a[i].x, w[j].x, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].y, w[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].z, w[j].z, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].w, w[j].w, acc[i][j]);
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + ty + 16 * i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias[n];
+            v = dd_activation(v, act);
+            if (residual) v += residual[(size_t)m * ldr + n];
+            C[(size_t)m * ldc + n] = v;
+        }
+    }
+}
+
+int launch_big(const void* A, int lda, const void* W, int ldw, const float* bias, const float* residual, int ldr,
+               void* C, int ldc, int M, int N, int K, int act, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_simt_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BG_SMEM);
+        if (e != cudaSuccess) return dd_fail("dd_gemm_simt: shared memory of %d bytes refused: %s", BG_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(dd_ceil_div(N, BG), dd_ceil_div(M, BG));
+    if (grid.y > 65535) return dd_fail("dd_gemm_simt: too many rows (%d)", M);
+    dd_launch(gemm_simt_big_kernel, grid, dim3(BG_THREADS), BG_SMEM, s, (const float*)A, lda, (const float*)W, ldw, bias, residual,
+              ldr, (float*)C, ldc, M, N, K, act);
+    return dd_check_launch("dd_gemm_simt");
+}
+
 template <typename TI, typename TO>
 int launch(const void* A, int lda, const void* W, int ldw, const float* bias, const float* residual, int ldr,
            void* C, int ldc, int M, int N, int K, int act, cudaStream_t s) {
@@ -185,7 +281,7 @@ DD_API int dd_gemm_simt(const void* A, int lda, const void* W, int ldw, const fl
     if (K <= 0) return dd_fail("dd_gemm_simt: bad K=%d", K);
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == DD_F32 && out_dtype == DD_F32) {
-        // up to 32 rows with 16-byte aligned rows: the kernel that streams the weights once
+        // up to 64 rows with 16-byte aligned rows: the kernel that streams the weights once; more rows: tiles of 128 x 128
         const bool aligned = K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && !(((uintptr_t)A | (uintptr_t)W) & 15);
         const bool narrow = N < 3200;                      // fewer than a hundred blocks of 32 features
         if (aligned && M <= 8) return narrow ? launch_rows<8, 16, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s)
@@ -194,6 +290,9 @@ DD_API int dd_gemm_simt(const void* A, int lda, const void* W, int ldw, const fl
                                               : launch_rows<16, 32, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s);
         if (aligned && M <= 32) return narrow ? launch_rows<32, 16, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s)
                                               : launch_rows<32, 32, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s);
+        if (aligned && M <= 64) return narrow ? launch_rows<64, 16, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s)
+                                              : launch_rows<64, 32, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s);
+        if (aligned) return launch_big(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s);
         return launch<float, float>(A, lda, W, ldw, bias, residual, ldr, C, ldc, M, N, K, act, s);
     }
     if (in_dtype == DD_BF16 && out_dtype == DD_F32)

@@ -58,7 +58,8 @@ def test_layernorm(K, dtype, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(37, 53, 45), (1, 130, 96), (70, 64, 320), (13, 200, 100), (30, 3300, 136), (40, 1600, 1600)])
+@pytest.mark.parametrize("shape", [(37, 53, 45), (1, 130, 96), (70, 64, 320), (13, 200, 100), (30, 3300, 136), (40, 1600, 1600),
+                                   (150, 200, 72), (300, 130, 1600)])
 def test_gemm_simt(K, dtype, shape):
     M, N, Kd = shape
     g = torch.Generator().manual_seed(2)
@@ -89,9 +90,9 @@ def test_gemm_simt(K, dtype, shape):
     alone = K.gemm_simt(a[3:4].contiguous() if M > 3 else a, w, bias)
     whole = K.gemm_simt(a, w, bias)
     assert torch.equal(alone[0], whole[3 if M > 3 else 0])
-    # ... nor on the kernel that the number of rows selects (up to 8, 16 and 32 rows stream the weights once; more
-    # rows run in tiles): the same bits
-    for m in (2, 8, 9, 16, 17, 32):
+    # ... nor on the kernel that the number of rows selects (up to 8, 16, 32 and 64 rows stream the weights once; more
+    # rows run in tiles of 128 x 128; operands that are not 16-byte aligned in tiles of 64 x 64): the same bits
+    for m in (2, 8, 9, 16, 17, 32, 33, 64, 65, 129):
         if m < M:
             assert torch.equal(K.gemm_simt(a[:m], w, bias), whole[:m]), f"{m} rows alone differ from the same rows among {M}"
 
