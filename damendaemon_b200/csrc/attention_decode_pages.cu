@@ -14,6 +14,9 @@
 // With k_new/v_new the step's own key and value replace the cache row of the token's position in shared memory
 // and are written to the cache by the warp that owns the head. Rows of the last page beyond the position are
 // zeroed in shared memory (values) or masked by index (scores), so stale cache contents never reach the result.
+// n_splits is the most splits a token's pages may be cut into (the grid's third dimension); when the grid then holds
+// more blocks than can be resident at once, the kernel gives each token its share of them, by its number of pages
+// among all tokens' pages (see the kernel), and the blocks beyond a token's count leave at once.
 // Every wait on a barrier is bounded (error bit 8).
 #include "common.cuh"
 #include "tcgen05.cuh"

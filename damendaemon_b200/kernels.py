@@ -417,7 +417,8 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
     at a time (see attention_decode_supported); 'pages': whole pages of a group of heads by TMA (see
     attention_decode_pages_supported). With k_new/v_new (row views of the buffer q lives in) the step's own keys and
     values are used from there and written into the cache by this kernel; otherwise they must be in the cache already.
-    token_entry None: token t belongs to entry t (a step of single tokens in entry order)."""
+    token_entry None: token t belongs to entry t (a step of single tokens in entry order). n_splits: into how many
+    pieces a token's keys are cut; for 'pages' the most a token may get (the kernel deals them out by context length)."""
     if kernel not in ("rows", "pages"):
         raise KernelError(f"attention_decode: unknown kernel {kernel!r}")
     n_pages, _, kv_heads, page_size, head_dim = cache.shape

@@ -418,3 +418,24 @@ def test_sampling(K):
     # a padded row stride is honoured
     wide = torch.zeros(3, V + 13); wide[:, :V] = rows[:3]; wide[:, V:] = 100.0
     assert K.sample(wide.to(DEV)[:, :V]).cpu().tolist() == [int(rows[i].argmax()) for i in range(3)]
+
+
+def test_early_launch_can_be_switched_for_a_stretch_of_launches(K):
+    """kernels.pdl_scope: programmatic dependent launch off (or on) inside, what was in force before afterwards, also
+    when scopes nest or an exception passes through; results do not depend on it."""
+    K.library("core")
+    x = torch.randn(9, 64, device=DEV)
+    w = torch.randn(40, 64, device=DEV)
+    assert K._pdl is True
+    with K.pdl_scope(False):
+        assert K._pdl is False
+        quiet = K.gemm_simt(x, w)
+        with K.pdl_scope(True):
+            assert K._pdl is True
+        assert K._pdl is False
+    assert K._pdl is True
+    with pytest.raises(ValueError):
+        with K.pdl_scope(False):
+            raise ValueError("passes through")
+    assert K._pdl is True
+    assert torch.equal(quiet, K.gemm_simt(x, w))
