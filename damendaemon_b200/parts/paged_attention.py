@@ -19,7 +19,9 @@ class AttentionTuning:
     """Thresholds of the kernel choice. The defaults were measured on a B200 with 25 heads of 64 and 768 keys per
     request: the page-streaming decode kernel wins from 8 requests on (11.6 against 14.0 us; 54 against 68 us at 64
     requests) and loses at 4 and below (11.0 against 9.8 us; 9.1 against 5.5 us at one request)."""
-    pages_from_pairs: int = 150           # decode steps with at least this many (token, head) pairs stream whole pages
+    pages_from_pairs: int = 150           # decode steps with at least this many (token, head) pairs stream whole pages,
+    pages_from_pair_keys: int = 200_000   # ... or with this many pairs x keys of context (one request of 16,384 keys:
+                                          # 36 us in pages, 45 us in rows; two of 4,096: 25 us either way; one: 22 / 15)
     pages_per_block: int = 128            # a block of the page-streaming kernel holds the ids of this many pages
     row_keys_per_block: int = 128         # key split of the row decode kernel: keys per block ...
     row_blocks_per_sm: int = 2            # ... and blocks wanted per SM
@@ -47,7 +49,10 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None):
     k_new, v_new = (k, v) if cache.writable else (None, None)
     fast = runtime.attention != "rows"
     tensor = fast and runtime.attention != "mma"
-    if ctx.decode_only and tensor and ctx.n_tokens * n_heads >= tune.pages_from_pairs and \
+    def wants_pages(n_tokens):
+        pairs = n_tokens * n_heads
+        return pairs >= tune.pages_from_pairs or pairs * ctx.split_context >= tune.pages_from_pair_keys
+    if ctx.decode_only and tensor and wants_pages(ctx.n_tokens) and \
             kernels.attention_decode_pages_supported(n_heads, kv_heads, head_dim, page_size, q.dtype):
         # whole pages of a group of heads by TMA; it takes the new keys and values from the projection and writes them
         splits = kernels.attention_decode_pages_splits(ctx.n_tokens, n_heads, page_size, ctx.split_context, q.device)
@@ -72,7 +77,7 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None):
     if n1:
         import torch
         out = torch.empty((q.shape[0], n_heads * head_dim), dtype=q.dtype, device=q.device)
-        pages = tensor and n1 * n_heads >= tune.pages_from_pairs and \
+        pages = tensor and wants_pages(n1) and \
             kernels.attention_decode_pages_supported(n_heads, kv_heads, head_dim, page_size, q.dtype)
         if pages:
             splits = kernels.attention_decode_pages_splits(n1, n_heads, page_size, ctx.split_context, q.device)
