@@ -305,11 +305,23 @@ def parity(layers):
     worst = lambda a, b: max(float((a[r] - b[r]).abs().max()) for r in requests)
     same = lambda a, b: sum(int((a[r].argmax(-1) == b[r].argmax(-1)).sum()) for r in requests)
     total = 33 * len(requests)
+
+    def widest_flipped_margin(a, b):
+        """Among rows whose greedy tokens differ: the largest gap between the reference's best and second-best logit
+        (a flip is a near tie if this is below the logit difference between the two engines)."""
+        gap = 0.0
+        for r in requests:
+            flipped = a[r].argmax(-1) != b[r].argmax(-1)
+            if bool(flipped.any()):
+                top = b[r][flipped].topk(2, dim=-1).values
+                gap = max(gap, float((top[:, 0] - top[:, 1]).max()))
+        return gap
     return {"parity": "GPT-2 XL shape, seeded random weights, 2 requests x (512-token prompt + 32 forced decode steps)",
             "n_layer_run": layers, "rows_compared": total,
             "float32_vs_plain_float64": {"max_abs_logit_diff": worst(got["float32"], want), "same_greedy": same(got["float32"], want)},
             "bfloat16_vs_float32": {"max_abs_logit_diff": worst(got["bfloat16"], got["float32"]),
-                                    "same_greedy": same(got["bfloat16"], got["float32"])},
+                                    "same_greedy": same(got["bfloat16"], got["float32"]),
+                                    "widest_top2_gap_where_greedy_differs": widest_flipped_margin(got["bfloat16"], got["float32"])},
             "logit_scale": float(max(v.abs().max() for v in want.values()))}
 
 
