@@ -39,6 +39,25 @@ def _gemm_case(name, tokens, dev):
     return run, work
 
 
+def _gemm32_case(name, tokens, dev):
+    """The same products in true 32-bit on the CUDA cores (float32 weights, activations and stream)."""
+    features, reduction, epilogue = SHAPES[name]
+    copies = max(2, min(12, (300 << 20) // (features * reduction * 4)))
+    weights = [torch.randn(features, reduction, device=dev).mul_(0.02) for _ in range(copies)]
+    bias = torch.randn(features, device=dev)
+    x = torch.randn(tokens, reduction, device=dev)
+    stream = torch.zeros(tokens, features, device=dev)
+    out = torch.empty(tokens, features, device=dev)
+
+    def run(i):
+        w = weights[i % copies]
+        if epilogue == "residual":
+            K.gemm_simt(x, w, bias, residual=stream, out=stream)
+        else:
+            K.gemm_simt(x, w, bias if epilogue != "none" else None, activation="gelu_new" if epilogue == "gelu" else None, out=out)
+    return run, {"bytes": features * reduction * 4, "flops": 2 * tokens * features * reduction}
+
+
 def _layernorm_case(rows, dev):
     """LayerNorm of `rows` rows of the float32 stream (width 1600) into bfloat16, as before every projection."""
     width = H * D
@@ -83,12 +102,14 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False):
 
 
 def build(name, device="cuda:0"):
-    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | attn_decode_b<batch>[_c<context>] (page streaming) | attn_decode_rows_b<batch>[_c<context>] | attn_prefill_p<prompts>_t<tokens> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
+    """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | gemm32_<...>_m<tokens> (float32, CUDA cores) | attn_decode_b<batch>[_c<context>] (page streaming) | attn_decode_rows_b<batch>[_c<context>] | attn_prefill_p<prompts>_t<tokens> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
     attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows>"""
     K.library("core"), K.library("tensor")
     parts = name.split("_")
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
         return _gemm_case(parts[1], int(parts[2][1:]), device)
+    if parts[0] == "gemm32" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
+        return _gemm32_case(parts[1], int(parts[2][1:]), device)
     if name.startswith("layernorm_m"):
         return _layernorm_case(int(name[len("layernorm_m"):]), device)
     if name.startswith("attn_decode_rows_b") or name.startswith("attn_decode_b"):
