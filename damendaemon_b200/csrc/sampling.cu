@@ -28,7 +28,28 @@ __device__ __forceinline__ Best better(Best a, Best b) {
 __device__ Best block_argmax(const float* row, int V, bool* saw_nan, Best* sh, int* sh_nan) {
     Best best{-CUDART_INF_F, 0x7fffffff};
     int nan = 0;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
+    // A row of an odd vocabulary starts anywhere: a few single values up to the first 16-byte boundary, then four values
+    // a load and four loads in flight per thread (one value a load, the scan of 50,257 logits took 11 us of a decode
+    // step), then the last few.
+    const int head = min(V, (int)(((16 - ((uintptr_t)row & 15)) & 15) >> 2));
+    const int n4 = (V - head) >> 2;
+    if ((int)threadIdx.x < head) {
+        const float v = row[threadIdx.x];
+        nan |= (v != v);
+        best = better(best, Best{v, (int)threadIdx.x});
+    }
+    const float4* body = reinterpret_cast<const float4*>(row + head);
+#pragma unroll 4
+    for (int j = threadIdx.x; j < n4; j += THREADS) {
+        const float4 v = body[j];
+        const int i = head + 4 * j;
+        nan |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+        best = better(best, Best{v.x, i});
+        best = better(best, Best{v.y, i + 1});
+        best = better(best, Best{v.z, i + 2});
+        best = better(best, Best{v.w, i + 3});
+    }
+    for (int i = head + 4 * n4 + threadIdx.x; i < V; i += THREADS) {
         const float v = row[i];
         nan |= (v != v);
         best = better(best, Best{v, i});
@@ -83,13 +104,13 @@ sample_kernel(const float* __restrict__ logits, int ldl, int V, const float* __r
     dd_grid_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ldl;
+    const float T = temperature ? temperature[r] : 0.f;       // asked for before the scan, not after it
     bool nan;
     const Best best = block_argmax(row, V, &nan, sh_best, sh_nan);
     if (nan || !(best.v > -CUDART_INF_F) || best.v == CUDART_INF_F) {
         if (threadIdx.x == 0) out[r] = -1;
         return;
     }
-    const float T = temperature ? temperature[r] : 0.f;
     if (!(T > 0.f)) {
         if (threadIdx.x == 0) out[r] = best.i;
         return;
